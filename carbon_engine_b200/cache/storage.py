@@ -17,7 +17,7 @@ import numpy as np
 import torch
 
 from .. import ops
-from ..parts.base import PagedCacheSpec, StateCacheSpec
+from ..parts.base import BundleCacheSpec, PagedCacheSpec, StateCacheSpec
 from ..parts.model import LayerCall
 from .manager import CacheManager, GroupSpec
 
@@ -32,6 +32,8 @@ class LayerCacheView:
     v_pool: Optional[torch.Tensor] = None
     state: Optional[torch.Tensor] = None        # [max_requests, *shape]
     writes: bool = True
+    #: named states of the block around the mixer (a ``BundleCacheSpec``'s ``extra``), each [max_requests, *shape]
+    extra: Optional[Dict[str, torch.Tensor]] = None
 
 
 class CacheStorage:
@@ -39,7 +41,12 @@ class CacheStorage:
                  max_requests: int, max_seq_len: int, window_pages: Optional[int] = None, poison: bool = False):
         self.device, self.dtype, self.page_size = device, dtype, int(page_size)
         self.max_requests = int(max_requests)
-        layout = model.cache_layout()
+        layout, extras = [], {}
+        for cache_id, spec in model.cache_layout():
+            if isinstance(spec, BundleCacheSpec):
+                extras[cache_id] = spec.extra
+                spec = spec.main
+            layout.append((cache_id, spec))
         # the block tables of all groups have one width: what the smallest page size needs
         smallest = min([page_size] + [s.page_size for _, s in layout if isinstance(s, PagedCacheSpec) and s.page_size])
         self.max_pages_per_request = (int(max_seq_len) + smallest - 1) // smallest
@@ -55,9 +62,8 @@ class CacheStorage:
                     # ``num_pages`` counts pages of the engine's size: a group with other pages holds as many tokens
                     groups.append(GroupSpec(ps, max(1, int(n) * int(page_size) // ps), int(spec.window)))
                 g = group_of[(spec.window, ps)]
-                shape = (groups[g].num_pages, spec.kv_heads, ps, spec.head_dim)
-                k = torch.empty(shape, dtype=dtype, device=device)
-                v = torch.empty(shape, dtype=dtype, device=device)
+                k = torch.empty((groups[g].num_pages, spec.kv_heads, ps, spec.head_dim), dtype=dtype, device=device)
+                v = torch.empty((groups[g].num_pages, spec.value_heads, ps, spec.value_dim), dtype=dtype, device=device)
                 if poison:          # stale reads then show up as NaN in the logits
                     k.fill_(float("nan")); v.fill_(float("nan"))
                 else:
@@ -68,6 +74,10 @@ class CacheStorage:
                 self._entries[cache_id] = LayerCacheView("state", state=st)
             else:
                 self._entries[cache_id] = LayerCacheView("none")
+            if cache_id in extras:
+                self._entries[cache_id].extra = {
+                    name: torch.zeros((max_requests, *st.shape), dtype=st.dtype or dtype, device=device)
+                    for name, st in extras[cache_id]}
         self.groups = groups
         self.manager = CacheManager(groups, max_requests, self.max_pages_per_request)
         self.device_tables = [torch.full((max_requests, self.max_pages_per_request), -1, dtype=torch.int32, device=device)
@@ -80,7 +90,7 @@ class CacheStorage:
         base = self._entries[call.cache]
         if call.writes:
             return base
-        return LayerCacheView(base.kind, base.group, base.page_size, base.k_pool, base.v_pool, base.state, False)
+        return LayerCacheView(base.kind, base.group, base.page_size, base.k_pool, base.v_pool, base.state, False, base.extra)
 
     def paged_views(self) -> List[LayerCacheView]:
         return [e for e in self._entries.values() if e.kind == "paged"]
@@ -89,7 +99,7 @@ class CacheStorage:
         total = 0
         for e in self._entries.values():
             if e.kind == "paged":
-                total += 2 * e.k_pool.shape[1] * e.k_pool.shape[3] * e.k_pool.element_size()
+                total += (e.k_pool.shape[1] * e.k_pool.shape[3] + e.v_pool.shape[1] * e.v_pool.shape[3]) * e.k_pool.element_size()
         return total
 
     def slot_opened(self, slot: int) -> None:
@@ -98,10 +108,13 @@ class CacheStorage:
 
     def state_bytes(self) -> int:
         """Bytes of the fixed-size per-request state tensors (all slots)."""
-        return sum(e.state.numel() * e.state.element_size() for e in self._entries.values() if e.kind == "state")
+        total = sum(e.state.numel() * e.state.element_size() for e in self._entries.values() if e.kind == "state")
+        return total + sum(t.numel() * t.element_size() for e in self._entries.values() for t in (e.extra or {}).values())
 
     def zero_state(self, slot: int) -> None:
         """Reset the fixed-size state of a slot for a new request."""
         for e in self._entries.values():
             if e.kind == "state":
                 e.state[slot].zero_()
+            for t in (e.extra or {}).values():
+                t[slot].zero_()

@@ -2,7 +2,8 @@
 
 The reference picks the model by ``model_type`` (src/config.rs:457-467) and lists the supported
 names in its error.  Here the first entry of ``architectures`` decides, ``model_type`` is the
-fallback, and the error lists what is registered.
+fallback, and the error lists what is registered.  A config that names its design with a single string
+under ``architecture`` is read the same way.
 """
 from __future__ import annotations
 
@@ -41,6 +42,8 @@ def registered_architectures() -> List[str]:
 
 def resolve_architecture(raw: Dict[str, Any]) -> Architecture:
     names = raw.get("architectures")
+    if names is None and isinstance(raw.get("architecture"), str):       # some designs name themselves with one string
+        names = [raw["architecture"]]
     if isinstance(names, list):
         for n in names:
             if n in _ARCHITECTURES:

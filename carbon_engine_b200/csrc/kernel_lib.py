@@ -41,6 +41,27 @@ _SIGNATURES = {
     "ce_argmax": (_i, [_p, _i, _i, _p, _p]),
     "ce_apply_penalties": (_i, [_p, _i, _p, _i, _p, _p]),
     "ce_scatter_i32": (_i, [_p, _p, _p, _i, _ll, _p]),
+    # x, coef, w, out, out_dtype, rows, R, S, W, groups, eps, stream
+    "ce_streams_norm": (_i, [_p, _p, _p, _p, _i, _p, _i, _i, _i, _i, _f, _p]),
+    # h, mu, state, out, out_dtype, positions, seq_of_token, seq_slot, q_start, T, W, stream
+    "ce_token_shift": (_i, [_p, _p, _p, _p, _i, _p, _p, _p, _p, _i, _i, _p]),
+    # h, state, seq_slot, q_start, B, W, stream
+    "ce_save_last_rows": (_i, [_p, _p, _p, _p, _i, _i, _p]),
+    # x, y, mix, c_out, bias, T, S, W, stream
+    "ce_streams_write": (_i, [_p, _p, _p, _p, _p, _i, _i, _i, _p]),
+    # x0, x, T, S, W, stream
+    "ce_streams_broadcast": (_i, [_p, _p, _i, _i, _i, _p]),
+    # out, dtype, bias, M, N, ld, stream
+    "ce_add_bias": (_i, [_p, _i, _p, _i, _i, _i, _p]),
+    # qkv, k_pool, v_pool, dtype, bias, cos, sin, positions, seq_of_token, seq_slot, block_table, status,
+    # T, stride, nq, nk, nv, d, dv, rd, page_size, max_pages, num_pages, max_pos, write_kv, stream
+    "ce_bias_rope_kvwrite": (_i, [_p, _p, _p, _i] + [_p] * 8 + [_i] * 13 + [_p]),
+    # q, k_pool, v_pool, gate, out, dtype, positions, seq_of_token, seq_slot, block_table, status, T, nh, nkv, d, dv,
+    # q_stride, gate_stride, page_size, max_pages, num_pages, window, chunk, scale, lambda, eps, out_scale, stream
+    "ce_diff_attention": (_i, [_p] * 5 + [_i] + [_p] * 5 + [_i] * 12 + [_f] * 4 + [_p]),
+    # proj, w2, w0, a_bias, norm_w, state, out, out_dtype, seq_slot, q_start, B, ld, off_r, off_k, off_v, off_a, off_g,
+    # off_z, H, d, L, eps, stream
+    "ce_general_delta": (_i, [_p] * 7 + [_i] + [_p] * 2 + [_i] * 11 + [_f, _p]),
 }
 
 

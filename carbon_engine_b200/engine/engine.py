@@ -145,17 +145,24 @@ class Engine:
 
     # -- sizing ---------------------------------------------------------------------------------
     def _bytes_per_token(self) -> int:
-        from ..parts.base import PagedCacheSpec
+        from ..parts.base import BundleCacheSpec, PagedCacheSpec
         el = 2 if self.dtype == torch.bfloat16 else 4
-        return sum(2 * s.kv_heads * s.head_dim * el for _, s in self.model.cache_layout()
+        specs = [s.main if isinstance(s, BundleCacheSpec) else s for _, s in self.model.cache_layout()]
+        return sum((s.kv_heads * s.head_dim + s.value_heads * s.value_dim) * el for s in specs
                    if isinstance(s, PagedCacheSpec))
 
     def _state_bytes(self) -> int:
         """Bytes of the fixed-size per-request state of every slot (src/model/mod.rs:129-145 counts them too)."""
-        from ..parts.base import StateCacheSpec
+        from ..parts.base import BundleCacheSpec, StateCacheSpec
         el = 2 if self.dtype == torch.bfloat16 else 4
         total = 0
+        specs = []
         for _, s in self.model.cache_layout():
+            if isinstance(s, BundleCacheSpec):
+                specs.extend(st for _, st in s.extra)
+                s = s.main
+            specs.append(s)
+        for s in specs:
             if isinstance(s, StateCacheSpec):
                 n = 1
                 for dim in s.shape:

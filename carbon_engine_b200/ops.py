@@ -272,6 +272,133 @@ def gemm_plain(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, mode: int) -> 
                                 mode, _stream()))
 
 
+def streams_norm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float, groups: int = 1,
+                 coef: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None) -> None:
+    """out[r] = RMS norm in ``groups`` equal parts of sum_s coef[s] x[row, s, :], times weight.  x float32
+    [T, W] or [T, S, W]; coef None: the plain sum of the streams."""
+    _need(x, "x", torch.float32); _need(weight, "weight", torch.float32); _need(out, "out")
+    R, W = out.shape
+    S = x.shape[1] if x.dim() == 3 else 1
+    if x.shape[-1] != W or weight.numel() != W:
+        raise KernelError(f"streams_norm: widths differ: x {tuple(x.shape)}, weight {tuple(weight.shape)}, out {tuple(out.shape)}")
+    if coef is not None:
+        _need(coef, "coef", torch.float32)
+        if coef.numel() != S:
+            raise KernelError(f"streams_norm: {coef.numel()} coefficients for {S} streams")
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+    _ok(kernels().ce_streams_norm(_ptr(x), _ptr(coef), _ptr(weight), _ptr(out), dtype_code(out.dtype), _ptr(rows), R, S, W,
+                                  int(groups), float(eps), _stream()))
+
+
+def token_shift(h: torch.Tensor, mu: torch.Tensor, state: torch.Tensor, out: torch.Tensor, positions, seq_of_token,
+                seq_slot, q_start) -> None:
+    """out[t] = h[t] + (previous row - h[t]) * mu; the previous row of a portion's first token is state[slot]
+    (zeros at position 0).  h and state float32."""
+    _need(h, "h", torch.float32); _need(mu, "mu", torch.float32); _need(state, "state", torch.float32); _need(out, "out")
+    T, W = h.shape
+    if out.shape != h.shape or mu.numel() != W or state.shape[-1] != W:
+        raise KernelError("token_shift: sizes differ")
+    _ok(kernels().ce_token_shift(_ptr(h), _ptr(mu), _ptr(state), _ptr(out), dtype_code(out.dtype), _ptr(positions),
+                                 _ptr(seq_of_token), _ptr(seq_slot), _ptr(q_start), T, W, _stream()))
+
+
+def save_last_rows(h: torch.Tensor, state: torch.Tensor, seq_slot: torch.Tensor, q_start: torch.Tensor) -> None:
+    """state[slot of sequence b] = h[last token of b] for every sequence of the step."""
+    _need(h, "h", torch.float32); _need(state, "state", torch.float32)
+    if state.shape[-1] != h.shape[1]:
+        raise KernelError("save_last_rows: widths differ")
+    _ok(kernels().ce_save_last_rows(_ptr(h), _ptr(state), _ptr(seq_slot), _ptr(q_start), seq_slot.numel(), h.shape[1],
+                                    _stream()))
+
+
+def streams_write(x: torch.Tensor, y: torch.Tensor, mix: torch.Tensor, c_out: torch.Tensor,
+                  bias: Optional[torch.Tensor] = None) -> None:
+    """x[t, to] <- sum_from mix[from, to] x[t, from] + c_out[to] (y[t] + bias), in place; x [T, S, W] float32."""
+    _need(x, "x", torch.float32); _need(y, "y", torch.float32); _need(mix, "mix", torch.float32)
+    _need(c_out, "c_out", torch.float32)
+    T, S, W = x.shape
+    if y.shape != (T, W) or mix.shape != (S, S) or c_out.numel() != S:
+        raise KernelError(f"streams_write: x {tuple(x.shape)}, y {tuple(y.shape)}, mix {tuple(mix.shape)} do not fit")
+    _ok(kernels().ce_streams_write(_ptr(x), _ptr(y), _ptr(mix), _ptr(c_out), _ptr(bias), T, S, W, _stream()))
+
+
+def streams_broadcast(x0: torch.Tensor, x: torch.Tensor) -> None:
+    """x[t, s] = x0[t] for every stream s."""
+    _need(x0, "x0", torch.float32); _need(x, "x", torch.float32)
+    T, S, W = x.shape
+    if x0.shape != (T, W):
+        raise KernelError("streams_broadcast: sizes differ")
+    _ok(kernels().ce_streams_broadcast(_ptr(x0), _ptr(x), T, S, W, _stream()))
+
+
+def add_bias(out: torch.Tensor, bias: torch.Tensor, n: Optional[int] = None) -> None:
+    """out[:, :n] += bias (float32), out float32 or bfloat16."""
+    _need(out, "out"); _need(bias, "bias", torch.float32)
+    n = bias.numel() if n is None else n
+    if n > out.shape[1] or n > bias.numel():
+        raise KernelError("add_bias: more columns than the output or the bias has")
+    _ok(kernels().ce_add_bias(_ptr(out), dtype_code(out.dtype), _ptr(bias), out.shape[0], n, out.stride(0), _stream()))
+
+
+def bias_rope_kvwrite(qkv, k_pool, v_pool, bias, cos, sin, positions, seq_of_token, seq_slot, block_table, status,
+                      nq: int, nk: int, nv: int, d: int, dv: int, rotary_dim: int, page_size: int,
+                      write_kv: bool = True) -> None:
+    """Rows [nq heads of d | nk heads of d | nv heads of dv | ...]: bias added, q and k rotated over their first
+    ``rotary_dim`` elements (element i with i + rotary_dim/2), q in place, k and v into the pages."""
+    _need(qkv, "qkv")
+    for name, t in (("bias", bias), ("cos", cos), ("sin", sin)):
+        if t is not None:
+            _need(t, name, torch.float32)
+    if bias is not None and bias.numel() < (nq + nk) * d + nv * dv:
+        raise KernelError("bias_rope_kvwrite: the bias is shorter than q|k|v")
+    if cos is not None and cos.shape[1] != rotary_dim // 2:
+        raise KernelError("bias_rope_kvwrite: rotary table width is not rotary_dim / 2")
+    if write_kv:
+        _need(k_pool, "k_pool", qkv.dtype); _need(v_pool, "v_pool", qkv.dtype)
+        if tuple(k_pool.shape[1:]) != (nk, page_size, d) or tuple(v_pool.shape[1:]) != (nv, page_size, dv):
+            raise KernelError(f"bias_rope_kvwrite: pools {tuple(k_pool.shape)} / {tuple(v_pool.shape)} do not fit "
+                              f"{nk} x {d} keys and {nv} x {dv} values in pages of {page_size}")
+    _ok(kernels().ce_bias_rope_kvwrite(
+        _ptr(qkv), _ptr(k_pool), _ptr(v_pool), dtype_code(qkv.dtype), _ptr(bias), _ptr(cos), _ptr(sin), _ptr(positions),
+        _ptr(seq_of_token), _ptr(seq_slot), _ptr(block_table), _ptr(status), qkv.shape[0], qkv.stride(0), nq, nk, nv, d, dv,
+        rotary_dim if cos is not None else 0, page_size, block_table.shape[1] if block_table is not None else 0,
+        k_pool.shape[0] if k_pool is not None else 0, cos.shape[0] if cos is not None else 0, 1 if write_kv else 0, _stream()))
+
+
+def diff_attention(q, q_stride: int, k_pool, v_pool, gate, gate_stride: int, out, positions, seq_of_token, seq_slot,
+                   block_table, status, nh: int, nkv: int, d: int, dv: int, page_size: int, window: int, chunk: int,
+                   scale: float, lam: float, eps: float, out_scale: float) -> None:
+    """Differential attention in float32 arithmetic: two softmax maps per head over the same values,
+    o = a1 - lam a2, unit RMS per head times ``out_scale``, times sigmoid(gate logit)."""
+    _need(k_pool, "k_pool"); _need(v_pool, "v_pool", k_pool.dtype); _need(out, "out", k_pool.dtype)
+    if q.dtype != k_pool.dtype:
+        raise KernelError("diff_attention: q and the cache differ in dtype")
+    if k_pool.shape[1] != 2 * nkv or k_pool.shape[3] != d or v_pool.shape[1] != nkv or v_pool.shape[3] != dv:
+        raise KernelError(f"diff_attention: pools {tuple(k_pool.shape)} / {tuple(v_pool.shape)} do not fit {nkv} key heads")
+    _ok(kernels().ce_diff_attention(
+        _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(gate), _ptr(out), dtype_code(out.dtype), _ptr(positions),
+        _ptr(seq_of_token), _ptr(seq_slot), _ptr(block_table), _ptr(status), out.shape[0], nh, nkv, d, dv, q_stride,
+        gate_stride, page_size, block_table.shape[1], k_pool.shape[0], int(window), int(chunk), float(scale), float(lam),
+        float(eps), float(out_scale), _stream()))
+
+
+def general_delta(proj, w2, w0, a_bias, norm_w, state, out, seq_slot, q_start, n_seqs: int, offsets: Sequence[int],
+                  heads: int, d: int, rank: int, eps: float) -> None:
+    """The generalized delta rule over each sequence's tokens of the step, from and to ``state``
+    [slots, heads, d, d] (float32).  ``proj`` float32 [T, ld] holds, at ``offsets`` (r, k, v, a, g, z), the
+    projections of every token; ``out`` [T, heads * d] receives the normed, gated outputs."""
+    _need(proj, "proj", torch.float32); _need(state, "state", torch.float32); _need(out, "out")
+    for name, t in (("w2", w2), ("w0", w0), ("a_bias", a_bias), ("norm_w", norm_w)):
+        _need(t, name, torch.float32)
+    if tuple(state.shape[1:]) != (heads, d, d) or out.shape[1] != heads * d or w2.shape != (heads * d, rank):
+        raise KernelError("general_delta: sizes do not fit")
+    off_r, off_k, off_v, off_a, off_g, off_z = (int(o) for o in offsets)
+    _ok(kernels().ce_general_delta(_ptr(proj), _ptr(w2), _ptr(w0), _ptr(a_bias), _ptr(norm_w), _ptr(state), _ptr(out),
+                                   dtype_code(out.dtype), _ptr(seq_slot), _ptr(q_start), n_seqs, proj.stride(0), off_r, off_k,
+                                   off_v, off_a, off_g, off_z, heads, d, rank, float(eps), _stream()))
+
+
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
     _need(logits, "logits", torch.float32); _need(out, "out", torch.int32)
     R, V = logits.shape

@@ -18,7 +18,7 @@ import torch
 
 from .. import ops
 from .base import Mixer, PagedCacheSpec, Part, TensorGetter, TensorSpec
-from .linear import ACCUM, STORE, Linear
+from .linear import ACCUM, STORE, STORE_F32, Linear
 from .rope import PositionEncoding
 
 
@@ -45,6 +45,7 @@ class AttentionPlan:
 
 class PagedAttention(Mixer):
     graph_safe = True       # reads positions, tables and lengths from device buffers only
+    can_store = True
     plan_key = "paged_attention"
     TILE, TILE_TC = 64, 128         # tokens per tile of the mma.sync and of the tcgen05 flash kernel
 
@@ -117,7 +118,7 @@ class PagedAttention(Mixer):
                              ctx.bufs.dev_section("paged_attention.tiles_tc"), nt_tc,
                              split_bucket((longest + per_split - 1) // per_split))
 
-    def forward(self, ctx, h: torch.Tensor, x: torch.Tensor, cache) -> None:
+    def forward(self, ctx, h: torch.Tensor, x: torch.Tensor, cache, accumulate: bool = True) -> None:
         T = h.shape[0]
         nh, nkv, d = self.heads, self.kv_heads, self.head_dim
         qkv = ctx.buffer((T, (nh + 2 * nkv) * d))
@@ -135,7 +136,7 @@ class PagedAttention(Mixer):
                             pairing=pos.pairing if pos is not None else "half")
         out = ctx.buffer((T, nh * d))
         self.attend(ctx, qkv, out, cache, table)
-        self.o.forward(out, x, ACCUM)
+        self.o.forward(out, x, ACCUM if accumulate else STORE_F32)
 
     def attend(self, ctx, qkv: torch.Tensor, out: torch.Tensor, cache, table: torch.Tensor) -> None:
         nh, nkv, d = self.heads, self.kv_heads, self.head_dim

@@ -16,7 +16,8 @@ import torch
 #: How random weights are drawn for a tensor, by the ``init`` of its :class:`TensorSpec`: kind -> (mean,
 #: standard deviation, kept in float32).  N(0, 0.02) for "linear" and "embedding", 1 + N(0, 0.1) for "norm"
 #: (norm weights are small and are stored in 32-bit).  A part with other needs registers a kind of its own.
-INIT_KINDS = {"linear": (0.0, 0.02, False), "embedding": (0.0, 0.02, False), "norm": (1.0, 0.1, True)}
+INIT_KINDS = {"linear": (0.0, 0.02, False), "embedding": (0.0, 0.02, False), "norm": (1.0, 0.1, True),
+              "bias": (0.0, 0.05, True)}
 
 
 def register_init_kind(name: str, mean: float, std: float, keep_float32: bool = False) -> None:
@@ -25,6 +26,8 @@ def register_init_kind(name: str, mean: float, std: float, keep_float32: bool = 
 
 @dataclass(frozen=True)
 class TensorSpec:
+    """A tensor a part needs.  A dimension of -1 is taken from the stored tensor (a size that the configuration
+    does not give); such a part cannot be given random weights."""
     name: str
     shape: Tuple[int, ...]
     init: str = "linear"
@@ -38,6 +41,17 @@ class PagedCacheSpec:
     head_dim: int
     window: int = 0
     page_size: Optional[int] = None
+    #: the value pool's heads and head size where they differ from the keys' (None: the same)
+    v_heads: Optional[int] = None
+    v_head_dim: Optional[int] = None
+
+    @property
+    def value_heads(self) -> int:
+        return self.kv_heads if self.v_heads is None else self.v_heads
+
+    @property
+    def value_dim(self) -> int:
+        return self.head_dim if self.v_head_dim is None else self.v_head_dim
 
 
 @dataclass(frozen=True)
@@ -48,7 +62,17 @@ class StateCacheSpec:
     dtype: Optional[torch.dtype] = None
 
 
-CacheSpec = Union[PagedCacheSpec, StateCacheSpec, None]
+@dataclass(frozen=True)
+class BundleCacheSpec:
+    """A layer that keeps more than its mixer's cache: ``main`` is the mixer's (paged, state or None), ``extra``
+    are named fixed-size states of the block around it (the previous token's activations, for instance),
+    as (name, StateCacheSpec) pairs.  The mixer sees ``main`` as always; the block finds the others in the
+    view's ``extra``."""
+    main: Union[PagedCacheSpec, StateCacheSpec, None]
+    extra: Tuple[Tuple[str, StateCacheSpec], ...] = ()
+
+
+CacheSpec = Union[PagedCacheSpec, StateCacheSpec, BundleCacheSpec, None]
 TensorGetter = Callable[[str], torch.Tensor]
 
 
@@ -126,7 +150,11 @@ class Mixer(Part):
     def forward(self, ctx, h: torch.Tensor, x: torch.Tensor, cache) -> None:
         """Read the normed activations ``h`` [T, width] and ADD the result into the float32 residual
         stream ``x`` [T, width].  ``cache`` is this call's view of the cache (or None), ``ctx`` the
-        step's :class:`carbon_engine_b200.engine.batch.StepContext`."""
+        step's :class:`carbon_engine_b200.engine.batch.StepContext`.
+
+        Parts that can also STORE their result (float32, into a buffer that holds nothing yet) take a keyword
+        ``accumulate=False`` and say so with ``can_store = True``: blocks whose residual is not a plain
+        sum (several streams) ask for that."""
         raise NotImplementedError
 
 
@@ -140,6 +168,11 @@ class Block(Part):
     """One layer: an arrangement of norms, a mixer and a feed-forward around the residual stream."""
 
     mixer: Mixer
+
+    def cache_spec(self) -> CacheSpec:
+        """What one call of this block keeps between steps: its mixer's cache, or a bundle of that and
+        states of the block's own."""
+        return self.mixer.cache_spec()
 
     def forward(self, ctx, x: torch.Tensor, cache) -> None:
         raise NotImplementedError

@@ -2,11 +2,11 @@
 (src/model/mod.rs:645-650)."""
 from __future__ import annotations
 
-from typing import List
+from typing import List, Optional
 
 import torch
 
-from .base import Block, FeedForward, Mixer, Norm, Part
+from .base import Block, BundleCacheSpec, FeedForward, Mixer, Norm, Part
 
 
 class PreNormBlock(Block):
@@ -26,3 +26,71 @@ class PreNormBlock(Block):
         self.mixer.forward(ctx, h, x, cache)
         self.ffn_norm.forward(x, h)
         self.ffn.forward(ctx, h, x)
+
+
+class StreamBlock(Block):
+    """Pre-norm with the options of a residual kept as several streams and of a token shift before the mixer:
+
+        u = sum_s c_in[s] x_s (or x);  h = norm(u);  h <- shift(h) (mixer only);  y = sublayer(h);
+        x_t <- sum_s mix[s, t] x_s + c_out[t] y   (or x += y)
+
+    ``ffn`` None: the layer has only the mixer.  ``connections``: the two sublayers' hyper-connections (None: a
+    plain residual [T, width]).  ``shift``: the token shift (None: the mixer reads the norm's output); its state,
+    the last normed row of every request, is kept beside the mixer's cache (``BundleCacheSpec``).  The norms take
+    ``coef=`` (:class:`carbon_engine_b200.parts.norm.GroupedRMSNorm`)."""
+
+    def __init__(self, width: int, mixer_norm: Norm, mixer: Mixer, ffn_norm: Optional[Norm] = None,
+                 ffn: Optional[FeedForward] = None, connections=None, shift=None):
+        if (ffn is None) != (ffn_norm is None):
+            raise ValueError("a feed-forward and its norm come together")
+        if connections is not None and len(connections) != (2 if ffn is not None else 1):
+            raise ValueError("one hyper-connection per sublayer")
+        self.width = int(width)
+        self.mixer_norm, self.mixer, self.ffn_norm, self.ffn = mixer_norm, mixer, ffn_norm, ffn
+        self.connections, self.shift = connections, shift
+        for part in (mixer, ffn):
+            if connections is not None and part is not None and not getattr(part, "can_store", False):
+                raise ValueError(f"{type(part).__name__} cannot store its output, which a residual in streams needs")
+
+    def children(self) -> List[Part]:
+        parts = [self.mixer_norm, self.mixer, self.ffn_norm, self.ffn, self.shift, *(self.connections or [])]
+        return [p for p in parts if p is not None]
+
+    def cache_spec(self):
+        main = self.mixer.cache_spec()
+        if self.shift is None:
+            return main
+        return BundleCacheSpec(main, (("shift", self.shift.state_spec()),))
+
+    def step_bytes(self, tokens: int, element_size: int) -> int:
+        h = tokens * self.width * (element_size + 4 + (4 if self.connections is not None else 0))
+        ffn = self.ffn.step_bytes(tokens, element_size) if self.ffn is not None else 0
+        return h + max(self.mixer.step_bytes(tokens, element_size), ffn)
+
+    def forward(self, ctx, x: torch.Tensor, cache) -> None:
+        T, W = x.shape[0], self.width
+        hc = self.connections
+        # the mixer
+        coef = hc[0].c_in if hc is not None else None
+        h = ctx.buffer((T, W))
+        if self.shift is not None:
+            hn = ctx.buffer((T, W), torch.float32)
+            self.mixer_norm.forward(x, hn, coef=coef)
+            self.shift.forward(ctx, hn, h, cache.extra["shift"])
+        else:
+            self.mixer_norm.forward(x, h, coef=coef)
+        if hc is None:
+            self.mixer.forward(ctx, h, x, cache)
+        else:
+            y = ctx.buffer((T, W), torch.float32)
+            self.mixer.forward(ctx, h, y, cache, accumulate=False)
+            hc[0].write(x, y)
+        # the feed-forward
+        if self.ffn is None:
+            return
+        self.ffn_norm.forward(x, h, coef=hc[1].c_in if hc is not None else None)
+        if hc is None:
+            self.ffn.forward(ctx, h, x)
+        else:
+            self.ffn.forward(ctx, h, y, accumulate=False)
+            hc[1].write(x, y)

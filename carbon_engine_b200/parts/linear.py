@@ -63,25 +63,56 @@ def matmul_nt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, sc
 
 
 class Linear(Part):
-    def __init__(self, in_features: int, out_features: Sequence[int], names: Sequence[str], init: str = "linear"):
+    def __init__(self, in_features: int, out_features: Sequence[int], names: Sequence[str], init: str = "linear",
+                 bias_names: Optional[Sequence[Optional[str]]] = None, pad_rows_to: int = 1):
+        """``bias_names``: per stored tensor the name of its bias, or None for a tensor without one (a part of
+        the concatenation without a bias gets zeros).  ``pad_rows_to``: rows of zeros are appended until the row
+        count is a multiple of this, so that the output's row stride keeps an alignment (``padded_out``)."""
         if len(out_features) != len(names):
             raise ValueError("one name per stored tensor")
+        if bias_names is not None and len(bias_names) != len(names):
+            raise ValueError("one bias name (or None) per stored tensor")
         self.in_features = int(in_features)
         self.out_features = [int(o) for o in out_features]
         self.names = list(names)
         self.init = init
+        self.bias_names = list(bias_names) if bias_names is not None and any(bias_names) else None
+        self.pad_rows_to = max(1, int(pad_rows_to))
         self.weight: Optional[torch.Tensor] = None
+        self.bias: Optional[torch.Tensor] = None         # float32 [padded_out], or None
 
     @property
     def total_out(self) -> int:
         return sum(self.out_features)
 
+    @property
+    def padded_out(self) -> int:
+        return (self.total_out + self.pad_rows_to - 1) // self.pad_rows_to * self.pad_rows_to
+
     def tensor_specs(self) -> List[TensorSpec]:
-        return [TensorSpec(n, (o, self.in_features), self.init) for n, o in zip(self.names, self.out_features)]
+        specs = [TensorSpec(n, (o, self.in_features), self.init) for n, o in zip(self.names, self.out_features)]
+        if self.bias_names is not None:
+            specs += [TensorSpec(b, (o,), "bias") for b, o in zip(self.bias_names, self.out_features) if b]
+        return specs
 
     def load(self, get: TensorGetter, device, dtype) -> None:
         parts = [to_device(get(n), device, dtype) for n in self.names]
+        self.out_features = [int(t.shape[0]) for t in parts]           # a size given as -1 is the stored tensor's
+        pad = self.padded_out - self.total_out
+        if pad:
+            parts.append(torch.zeros((pad, self.in_features), dtype=dtype, device=device))
         self.weight = parts[0] if len(parts) == 1 else torch.cat(parts, dim=0).contiguous()
+        if self.bias_names is not None:
+            bias = [get(b).to(device).to(torch.float32) if b else torch.zeros(o, dtype=torch.float32, device=device)
+                    for b, o in zip(self.bias_names, self.out_features)]
+            if pad:
+                bias.append(torch.zeros(pad, dtype=torch.float32, device=device))
+            self.bias = torch.cat(bias).contiguous()
 
-    def forward(self, a: torch.Tensor, out: torch.Tensor, mode: int = STORE) -> None:
+    def forward(self, a: torch.Tensor, out: torch.Tensor, mode: int = STORE, add_bias: bool = True) -> None:
+        """``add_bias=False``: the caller adds ``self.bias`` itself (in a kernel that touches the output anyway)."""
         matmul_nt(a, self.weight, out, mode)
+        if add_bias and self.bias is not None and a.shape[0] > 0:
+            if mode == SWIGLU:
+                raise ValueError("a bias before the SwiGLU epilogue is not supported")
+            ops.add_bias(out, self.bias)

@@ -3,22 +3,26 @@
 weights are held as one matrix so that one product with a SwiGLU epilogue serves both."""
 from __future__ import annotations
 
-from typing import List
+from typing import List, Sequence
 
 import torch
 
 from .base import FeedForward, Part
-from .linear import ACCUM, SWIGLU, Linear
+from .linear import ACCUM, STORE_F32, SWIGLU, Linear
 
 
 class GatedMLP(FeedForward):
-    def __init__(self, hidden: int, intermediate: int, prefix: str, activation: str = "silu"):
+    can_store = True
+
+    def __init__(self, hidden: int, intermediate: int, prefix: str, activation: str = "silu",
+                 names: Sequence[str] = ("gate_proj.weight", "up_proj.weight", "down_proj.weight")):
+        """``names``: the gate, up and down tensors' names under ``prefix``."""
         if activation != "silu":
             raise ValueError(f"activation '{activation}' is not supported (silu only)")
         self.hidden, self.intermediate, self.prefix = hidden, intermediate, prefix
-        self.gate_up = Linear(hidden, [intermediate, intermediate],
-                              [f"{prefix}.gate_proj.weight", f"{prefix}.up_proj.weight"])
-        self.down = Linear(intermediate, [hidden], [f"{prefix}.down_proj.weight"])
+        gate, up, down = names
+        self.gate_up = Linear(hidden, [intermediate, intermediate], [f"{prefix}.{gate}", f"{prefix}.{up}"])
+        self.down = Linear(intermediate, [hidden], [f"{prefix}.{down}"])
 
     def children(self) -> List[Part]:
         return [self.gate_up, self.down]
@@ -26,7 +30,7 @@ class GatedMLP(FeedForward):
     def step_bytes(self, tokens: int, element_size: int) -> int:
         return tokens * self.intermediate * element_size
 
-    def forward(self, ctx, h: torch.Tensor, x: torch.Tensor) -> None:
+    def forward(self, ctx, h: torch.Tensor, x: torch.Tensor, accumulate: bool = True) -> None:
         act = ctx.buffer((h.shape[0], self.intermediate))
         self.gate_up.forward(h, act, SWIGLU)
-        self.down.forward(act, x, ACCUM)
+        self.down.forward(act, x, ACCUM if accumulate else STORE_F32)

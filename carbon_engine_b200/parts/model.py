@@ -28,8 +28,11 @@ def plain_schedule(n_blocks: int) -> List[LayerCall]:
 
 class DecoderModel(Part):
     def __init__(self, config, embedding: Embedding, blocks: Sequence[Block], head: LMHead,
-                 schedule: Optional[Sequence[LayerCall]] = None):
+                 schedule: Optional[Sequence[LayerCall]] = None, streams: int = 0):
+        """``streams`` > 0: the residual is kept as that many copies [T, streams, width], all equal to the
+        embedding at the start; the blocks read and write them, the head's norm reads their sum."""
         self.config = config
+        self.streams = int(streams)
         self.embedding = embedding
         self.blocks = list(blocks)
         self.head = head
@@ -62,7 +65,7 @@ class DecoderModel(Part):
         """(cache id, spec) for every cache of the schedule, taken from the mixer that writes it."""
         out = []
         for cache_id in sorted(self._writers):
-            spec: CacheSpec = self.blocks[self._writers[cache_id]].mixer.cache_spec()
+            spec: CacheSpec = self.blocks[self._writers[cache_id]].cache_spec()
             out.append((cache_id, spec))
         return out
 
@@ -70,18 +73,28 @@ class DecoderModel(Part):
         """Activations of a step of ``tokens`` tokens with logits at ``rows`` places: the float32 residual
         stream, the largest block's buffers (blocks run one after another), the normed rows and the logits."""
         blocks = max((b.step_bytes(tokens, element_size) for b in self.blocks), default=0)
-        return tokens * self.embedding.width * 4 + blocks + rows * (self.head.width * element_size + self.head.vocab * 4)
+        return tokens * self.embedding.width * 4 * (1 + self.streams) + blocks \
+            + rows * (self.head.width * element_size + self.head.vocab * 4)
 
     def load_weights(self, get, device: torch.device, dtype: torch.dtype) -> None:
         self.device, self.dtype = device, dtype
         self.load_all(get, device, dtype)
 
-    def forward(self, ctx, caches) -> torch.Tensor:
-        """Run all tokens of the step through the schedule; returns the residual stream [T, width]."""
+    def forward(self, ctx, caches, tap=None) -> torch.Tensor:
+        """Run all tokens of the step through the schedule; returns the residual stream [T, width]
+        ([T, streams, width] for a model with several).  ``tap(i, x)`` is called after the i-th call of
+        the schedule (for tests and for looking at a layer's output)."""
         x = torch.empty((ctx.T, self.embedding.width), dtype=torch.float32, device=self.device)
         self.embedding.forward(ctx, x)
-        for call in self.schedule:
+        if self.streams > 0:
+            from .. import ops
+            xs = torch.empty((ctx.T, self.streams, self.embedding.width), dtype=torch.float32, device=self.device)
+            ops.streams_broadcast(x, xs)
+            x = xs
+        for i, call in enumerate(self.schedule):
             self.blocks[call.block].forward(ctx, x, caches.view(call))
+            if tap is not None:
+                tap(i, x)
         return x
 
     def logits(self, ctx, x: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:

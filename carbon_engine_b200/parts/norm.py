@@ -1,6 +1,10 @@
 """RMSNorm: y = x * (1 / sqrt(mean(x^2) + eps)) * weight, the weight used as stored (no "+1")
 (src/model/layers.rs:117-146).  The weight is held in float32 whatever it was stored in; the sum of
-squares and the scaling are float32."""
+squares and the scaling are float32.
+
+:class:`GroupedRMSNorm` takes the norm in equal consecutive parts of the width, each part divided by its
+own root mean square, and can read a residual kept as several streams: the weighted (or plain) sum of the
+streams is formed, normalised and scaled in one kernel."""
 from __future__ import annotations
 
 from typing import List, Optional
@@ -24,3 +28,24 @@ class RMSNorm(Norm):
 
     def forward(self, x: torch.Tensor, out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
         ops.rmsnorm(x, self.weight, out, self.eps, rows)
+
+
+class GroupedRMSNorm(Norm):
+    """y = w * concat_g(part_g / sqrt(mean(part_g^2) + eps)) over ``groups`` equal parts of the width.  ``x`` may
+    be [T, width] or [T, streams, width]; with streams, ``coef`` [streams] weights their sum (None: plain sum)."""
+
+    def __init__(self, width: int, eps: float, name: str, groups: int = 1):
+        if groups <= 0 or width % groups:
+            raise ValueError(f"a width of {width} cannot be normalised in {groups} equal parts")
+        self.width, self.eps, self.name, self.groups = int(width), float(eps), name, int(groups)
+        self.weight: Optional[torch.Tensor] = None
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        return [TensorSpec(self.name, (self.width,), "norm")]
+
+    def load(self, get: TensorGetter, device, dtype) -> None:
+        self.weight = get(self.name).to(device).to(torch.float32).contiguous()
+
+    def forward(self, x: torch.Tensor, out: torch.Tensor, rows: Optional[torch.Tensor] = None,
+                coef: Optional[torch.Tensor] = None) -> None:
+        ops.streams_norm(x, self.weight, out, self.eps, self.groups, coef, rows)

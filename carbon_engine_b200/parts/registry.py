@@ -8,8 +8,10 @@ from __future__ import annotations
 from typing import Callable, Dict
 
 from .attention import PagedAttention
+from .delta_rule import GeneralDeltaRule
+from .diff_attention import DifferentialAttention
 from .mlp import GatedMLP
-from .norm import RMSNorm
+from .norm import GroupedRMSNorm, RMSNorm
 from .rope import NoPositionEncoding, RotaryEmbedding
 
 _KINDS: Dict[str, Dict[str, Callable]] = {"mixer": {}, "feed_forward": {}, "norm": {}, "position": {}}
@@ -42,7 +44,10 @@ def register_position(name, factory, replace=False): register_part("position", n
 
 register_mixer("full_attention", lambda **kw: PagedAttention(**{**kw, "window": 0}))
 register_mixer("sliding_attention", lambda **kw: PagedAttention(**kw))
+register_mixer("differential_attention", DifferentialAttention)
+register_mixer("general_delta", GeneralDeltaRule)
 register_feed_forward("gated_mlp", GatedMLP)
 register_norm("rmsnorm", RMSNorm)
+register_norm("grouped_rmsnorm", GroupedRMSNorm)
 register_position("rotary", RotaryEmbedding)
 register_position("none", lambda **kw: NoPositionEncoding())

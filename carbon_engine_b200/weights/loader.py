@@ -55,7 +55,8 @@ def check_tensors(specs: Sequence[TensorSpec], directory: TensorDirectory, ignor
     wrong_dtype: List[str] = []
     for n, s in expected.items():
         if n in have:
-            if tuple(directory.shape(n)) != tuple(s.shape):
+            stored = tuple(directory.shape(n))
+            if len(stored) != len(s.shape) or any(w != -1 and w != g for w, g in zip(s.shape, stored)):
                 wrong_shape.append(f"{n}: stored {list(directory.shape(n))}, model wants {list(s.shape)}")
             if directory.dtype(n) not in _FLOATS:
                 wrong_dtype.append(f"{n}: {directory.dtype(n)}")

@@ -57,6 +57,9 @@ def standard_normal(name: str, numel: int, seed: int, device, start: int = 0) ->
 def random_tensor(spec: TensorSpec, seed: int, device, dtype: torch.dtype, chunk: int = 1 << 24) -> torch.Tensor:
     numel = 1
     for s in spec.shape:
+        if s < 0:
+            raise ValueError(f"{spec.name}: a size of this tensor comes from a checkpoint; name it in the configuration "
+                             f"to draw random weights")
         numel *= s
     out = torch.empty(numel, dtype=dtype, device=device)
     try:
