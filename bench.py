@@ -149,6 +149,62 @@ def serve_workload(args, BenchHarness) -> int:
     return 0
 
 
+# Layer sizes for the comparison of the two designs: width, query heads, key/value heads, feed-forward width
+COMPARE_SIZES = {"1b": (2048, 16, 4, 6144), "4b": (2560, 20, 4, 9728), "8b": (4096, 32, 8, 12288)}
+
+
+def munizen_config(width, heads, kv_heads, ff, layers, vocab):
+    """A Munizen model whose layers alternate between the recurrent mixer and differential attention, every
+    layer with a feed-forward: per layer the same projection and feed-forward sizes as the Qwen3 model beside it
+    (a query head's two maps of 64 take the place of one head of 128; state heads of 64)."""
+    from carbon_engine_b200.config.munizen import MunizenConfig
+    attn = {"type": "attention", "mlp": {"kind": "dense", "ff": ff},
+            "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": 64, "vdim": 128, "diff": 0.3, "scale": 0.125,
+                      "rot": {"dims": 32, "base": 1e6}, "mask": {"size": 1024}}}
+    delta = {"type": "general_delta", "mlp": {"kind": "dense", "ff": ff},
+             "mixer": {"heads": width // 64, "dim": 64, "rank": 64}}
+    return MunizenConfig.from_dict({"architecture": "Munizen", "vocab": vocab, "width": width,
+                                    "layers": [delta if i % 2 == 0 else attn for i in range(layers)],
+                                    "norm": {"eps": 1e-6, "groups": 2}, "streams": 2, "max_position_embeddings": 8192})
+
+
+def compare_designs(args, BenchHarness, pk) -> int:
+    """Prefill and decode throughput of the Munizen design beside the Qwen3 dense design at equal layer sizes
+    (random weights, a few layers), with the kernels of each and their distance from the roofline."""
+    import torch
+    layers = args.layers if args.layers != SIZES_8B["num_hidden_layers"] else 4
+    vocab, out = 32768, {}
+    for name in args.sizes.split(","):
+        width, heads, kv_heads, ff = COMPARE_SIZES[name]
+        qwen = dict(SIZES_8B, num_hidden_layers=layers, hidden_size=width, num_attention_heads=heads,
+                    num_key_value_heads=kv_heads, head_dim=128, intermediate_size=ff, vocab_size=vocab, max_position_embeddings=8192)
+        row = {}
+        for design, cfg in (("munizen", munizen_config(width, heads, kv_heads, ff, layers, vocab)), ("qwen3", qwen)):
+            h = BenchHarness(cfg, max_batch=max(args.batch, 2), context=args.context, new_tokens=256, graphs=not args.no_graphs,
+                             step_tokens=max(4096, args.prefill_tokens))
+            pf = h.prefill(args.prefill_tokens, 3, 2)
+            dec = h.decode(args.batch, args.steps, args.warmup)
+            r = {"prefill_tokens_per_s": round(args.prefill_tokens / (pf["ms"] / 1e3), 1), "prefill_ms": round(pf["ms"], 3),
+                 "decode_tokens_per_s": round(dec["tokens_per_s"], 1), "decode_ms_per_step": round(dec["ms_per_step"], 4)}
+            if args.profile:
+                prof = h.profile(args.batch, args.prefill_tokens, pk["hbm_gbs"], pk["bf16_tflops"])
+                r["kernels"] = {part: [dict(k) for k in prof[part]["kernels"]] for part in ("decode", "prefill")}
+                for part in ("decode", "prefill"):
+                    print(f"\n{design} {name}, {part}: {prof[part]['us']:.0f} us with kernels one after another", file=sys.stderr)
+                    for k in prof[part]["kernels"]:
+                        frac = "" if k["frac_of_peak"] is None else f"{k['frac_of_peak']:.3f}"
+                        print(f"{k['kernel'][:58]:58s} {k['launches']:6d} {k['us']:10.1f} {k['share']:6.3f} {k['gb_s']:8.0f} "
+                              f"{k['tflop_s']:8.1f} {frac:>8s}", file=sys.stderr)
+            row[design] = r
+            del h
+            torch.cuda.empty_cache()
+        out[name] = row
+    print(json.dumps({"workload": "compare-designs", "layers": layers, "batch": args.batch, "context": args.context,
+                      "prefill_tokens": args.prefill_tokens, "dtype": "bf16", "peaks": pk["source"],
+                      "data": "synthetic: seeded random weights, seeded uniform-random token ids", "sizes": out}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -171,11 +227,15 @@ def main() -> int:
                     help="instead of the contract's line: the device activities between two decode steps through the entry "
                          "point (pick, read-back copies, upload, token copy) and the steps' period")
     ap.add_argument("--no-check", action="store_true", help="skip the comparison of a short greedy continuation with float32")
-    ap.add_argument("--workload", default="decode", choices=["decode", "mixed-14b", "batch16-32b"],
+    ap.add_argument("--sizes", default="1b,8b", help="with --workload compare-designs: which of the layer sizes "
+                    "1b, 4b, 8b (width / heads / feed-forward of models of about that size), with commas between them")
+    ap.add_argument("--workload", default="decode", choices=["decode", "mixed-14b", "batch16-32b", "compare-designs"],
                     help="decode: the contract's line (default).  mixed-14b: 32 requests with prompts of 128 to 3,072 tokens at "
                          "Qwen3-14B sizes, prompts cut under a 2,048-token step budget beside the decoding requests, 128 new "
                          "tokens each.  batch16-32b: 16 prompts of 1,024 tokens at Qwen3-32B sizes, 256 new tokens each.  Both "
-                         "run through the scheduler and print a line of their own")
+                         "run through the scheduler and print a line of their own.  compare-designs: prefill and decode throughput of "
+                         "the Munizen design beside the Qwen3 dense design at equal layer sizes (--sizes, --layers, default 4; "
+                         "with --profile also every kernel of both against the roofline)")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "the reference is a Rust crate on the candle library: no "
@@ -190,6 +250,8 @@ def main() -> int:
     import torch
     from carbon_engine_b200.bench_support import BenchHarness
     pk = peaks()
+    if args.workload == "compare-designs":
+        return compare_designs(args, BenchHarness, pk)
     if args.workload != "decode":
         return serve_workload(args, BenchHarness)
     cfg = dict(SIZES_8B, num_hidden_layers=args.layers)

@@ -16,10 +16,15 @@ from .sampling.params import SamplingParams
 
 
 class BenchHarness:
-    def __init__(self, cfg: Dict, max_batch: int, context: int, new_tokens: int, graphs: bool = True,
+    def __init__(self, cfg, max_batch: int, context: int, new_tokens: int, graphs: bool = True,
                  page_size: int = 64, seed: int = 0, step_tokens: int = 4096):
-        raw = dict(cfg, architectures=["Qwen3ForCausalLM"], model_type="qwen3")
-        self.config = Qwen3Config.from_dict(raw)
+        """``cfg``: the sizes of a Qwen3 dense model as a dict, or a typed configuration of any registered
+        architecture."""
+        if isinstance(cfg, dict):
+            raw = dict(cfg, architectures=["Qwen3ForCausalLM"], model_type="qwen3")
+            self.config = Qwen3Config.from_dict(raw)
+        else:
+            self.config = cfg
         self.context, self.new_tokens, self.page_size, self.max_batch = context, new_tokens, page_size, max_batch
         self.seed = seed
         per_seq = (context + new_tokens + page_size - 1) // page_size * page_size

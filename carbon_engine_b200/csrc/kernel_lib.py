@@ -59,9 +59,15 @@ _SIGNATURES = {
     # q, k_pool, v_pool, gate, out, dtype, positions, seq_of_token, seq_slot, block_table, status, T, nh, nkv, d, dv,
     # q_stride, gate_stride, page_size, max_pages, num_pages, window, chunk, scale, lambda, eps, out_scale, stream
     "ce_diff_attention": (_i, [_p] * 5 + [_i] + [_p] * 5 + [_i] * 12 + [_f] * 4 + [_p]),
-    # proj, w2, w0, a_bias, norm_w, state, out, out_dtype, seq_slot, q_start, B, ld, off_r, off_k, off_v, off_a, off_g,
-    # off_z, H, d, L, eps, stream
-    "ce_general_delta": (_i, [_p] * 7 + [_i] + [_p] * 2 + [_i] * 11 + [_f, _p]),
+    "ce_diff_attention_mma_supported": (_i, [_i, _i, _i]),
+    # q, k_pool, v_pool, gate, out, positions, seq_slot, q_start, block_table, tiles, status, n_tiles, nh, nkv, d, dv,
+    # q_stride, gate_stride, page_size, max_pages, num_pages, window, chunk, scale, lambda, eps, out_scale, stream
+    "ce_diff_attention_mma": (_i, [_p] * 11 + [_i] * 12 + [_f] * 4 + [_p]),
+    # proj, out, out_dtype, T, ld, off, L, stream
+    "ce_tanh_cols": (_i, [_p, _p, _i, _i, _i, _i, _i, _p]),
+    # proj, zz, w0, a_bias, norm_w, prep, raw, state, out, out_dtype, seq_slot, q_start, T, B, ld, off_r, off_k, off_v,
+    # off_a, off_g, H, d, eps, stream
+    "ce_general_delta": (_i, [_p] * 9 + [_i] + [_p] * 2 + [_i] * 10 + [_f, _p]),
 }
 
 

@@ -3,58 +3,146 @@
 //
 //     S_t = diag(w_t) S_{t-1} - (a_t * u_t) (u_t^T S_{t-1}) + k_t v_t^T        o_t = S_t^T r_t
 //
-// with the decay w_t = exp(-exp(-1/2) sigmoid(W2 tanh(z_t) + w0)) per key channel (z_t: a narrow
-// projection of the token), the removal rate a_t = sigmoid(a_raw + bias), and the unit key
+// with the decay w_t = exp(-exp(-1/2) sigmoid(z_t + w0)) per key channel (z_t: the token's decay logits, a
+// product of their own), the removal rate a_t = sigmoid(a_raw + bias), and the unit key
 // u_t = k_t / sqrt(sum k_t^2 + 1e-6).  Both the decay and the removal read the OLD state.  Afterwards
 // every head's o_t is divided by its root mean square, multiplied by a weight and by sigmoid(gate).
 //
-// One block per (head, sequence) walks the sequence's tokens of this step in order, from the state its
-// slot holds, and stores the state back.  The columns of S are independent of one another, so a column
-// lives in the registers of DR_R neighbouring lanes (each holds every DR_R-th row); the two sums over
-// rows a token needs (u^T S and S^T r) are a per-thread run plus a butterfly over those lanes: the
-// order of every sum depends on d only.  The per-token vectors of a tile of tokens (decays, rates, unit
-// keys) are prepared by all threads together before the walk.  Everything is float32.
+// Three kernels, all float32:
+//   prepare  every token on its own: w_t, u_t and a_t * u_t of every head               (parallel over tokens)
+//   walk     one block per (head, sequence, slice of value channels) walks the sequence's tokens of this
+//            step in order, from the state its slot holds, and stores the state back        (the recurrence)
+//   finish   every (token, head): root mean square, weight, gate, one rounding at the store   (parallel)
+//
+// The columns of S (value channels) are independent of one another, so a slice of DR_COLS columns is a block
+// of its own and a column lives in the registers of DR_R neighbouring lanes (each holds every DR_R-th
+// row); the two sums over rows a token needs (u^T S and S^T r) are a per-thread run plus a butterfly over
+// those lanes: the order of every sum depends on d only, never on how the tokens were cut into steps.  The
+// per-token vectors arrive in shared memory a tile of tokens ahead of the walk (cp.async, two buffers).
 #include "common.cuh"
 
-#define DR_R 4                   // lanes that share a column of the state
+#define DR_R 8                   // lanes that share a column of the state
+#define DR_COLS 16               // value channels a block walks
+#define DR_TILE 16               // tokens a buffer holds
+
+__device__ __forceinline__ float dr_sigmoid(float z) { return 1.0f / (1.0f + expf(-z)); }
+
+// out[t, l] = tanh(proj[t, off + l]) in the activation dtype: the input of the decay's second product
+template <typename T>
+__global__ void tanh_cols_kernel(const float* __restrict__ proj, T* __restrict__ out, int ld, int off, int L, size_t total) {
+    ce_pdl_begin();
+    size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += stride) {
+        size_t t = e / L;
+        int l = (int)(e % L);
+        CeType<T>::store(out + e, tanhf(proj[t * ld + off + l]));
+    }
+}
+
+extern "C" int ce_tanh_cols(const float* proj, void* out, int out_dtype, int T, int ld, int off, int L, cudaStream_t stream) {
+    if (T == 0 || L == 0) return CE_OK;
+    if (!proj || !out) return ce_fail(CE_ERR_ARG, "ce_tanh_cols: null pointer");
+    size_t total = (size_t)T * L;
+    int blocks = (int)((total + 255) / 256 < (size_t)148 * 8 ? (total + 255) / 256 : (size_t)148 * 8);
+    if (out_dtype == CE_F32) { ce_note("tanh_cols_kernel"); ce_launch(tanh_cols_kernel<float>, blocks, 256, 0, stream, proj, (float*)out, ld, off, L, total); }
+    else if (out_dtype == CE_BF16) { ce_note("tanh_cols_kernel"); ce_launch(tanh_cols_kernel<__nv_bfloat16>, blocks, 256, 0, stream, proj, (__nv_bfloat16*)out, ld, off, L, total); }
+    else return ce_fail(CE_ERR_ARG, "ce_tanh_cols: unknown dtype %d", out_dtype);
+    return ce_check_launch("ce_tanh_cols");
+}
 
 struct DeltaArgs {
-    const float* proj;           // [T, ld]: one product's output row, columns at the offsets below
-    const float* w2;             // [H*d, L]
+    const float* proj;           // [T, ld]: r, k, v, a, g at the column offsets below
+    const float* zz;             // [T, H*d] decay logits before w0
     const float* w0;             // [H*d]
     const float* a_bias;         // [H*d]
     const float* norm_w;         // [H*d]
+    float* prep;                 // [T, 3, H*d]: decay, unit key, rate x unit key
+    float* raw;                  // [T, H*d] o_t before the norm
     float* state;                // [slots, H, d, d]
     void* out;                   // [T, H*d]
     const int* seq_slot;
     const int* q_start;
-    int ld, off_r, off_k, off_v, off_a, off_g, off_z, H, d, L, tile;
+    int ld, off_r, off_k, off_v, off_a, off_g, H, d;
     float eps;
 };
 
-__device__ __forceinline__ float dr_sigmoid(float z) { return 1.0f / (1.0f + expf(-z)); }
+// One block per token, a warp per head in turn.
+__global__ void delta_prepare_kernel(DeltaArgs a) {
+    ce_pdl_begin();
+    int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    int d = a.d, n = a.H * d;
+    const float* row = a.proj + (size_t)t * a.ld;
+    const float* zr = a.zz + (size_t)t * n;
+    float* pw = a.prep + (size_t)t * 3 * n;
+    const float decay_rate = 0.60653065971263342f;       // exp(-1/2)
+    for (int h = warp; h < a.H; h += nwarp) {
+        float ss = 0.f;
+        for (int c = lane; c < d; c += 32) {
+            float k = row[a.off_k + h * d + c];
+            ss = fmaf(k, k, ss);
+        }
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        float inv = 1.0f / sqrtf(ss + 1e-6f);
+        for (int c = lane; c < d; c += 32) {
+            int col = h * d + c;
+            float u = row[a.off_k + col] * inv;
+            pw[col] = expf(-decay_rate * dr_sigmoid(zr[col] + a.w0[col]));
+            pw[n + col] = u;
+            pw[2 * n + col] = dr_sigmoid(row[a.off_a + col] + a.a_bias[col]) * u;
+        }
+    }
+}
 
-template <typename T, int RPT>
-__global__ void __launch_bounds__(DR_R * DR_R * RPT) general_delta_kernel(DeltaArgs a) {
+__device__ __forceinline__ void dr_cp4(float* dst, const float* src) {
+    unsigned s = (unsigned)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(s), "l"(src));
+}
+__device__ __forceinline__ void dr_cp16(float* dst, const float* src) {
+    unsigned s = (unsigned)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(src));
+}
+
+// Copies of one tile of tokens into a buffer: five vectors of d per token and DR_COLS values.
+template <bool VEC>
+__device__ __forceinline__ void dr_stage(const DeltaArgs& a, float* buf, int t0, int n_tok, int h, int col0, int ncols) {
+    int d = a.d, n = a.H * d, tid = threadIdx.x, nthr = blockDim.x;
+    float* vbuf = buf + 5 * DR_TILE * d;
+    if (VEC) {
+        int d4 = d >> 2;
+        for (int e = tid; e < 5 * n_tok * d4; e += nthr) {
+            int which = e / (n_tok * d4), rem = e % (n_tok * d4), tok = rem / d4, c = (rem % d4) * 4;
+            size_t t = (size_t)(t0 + tok);
+            const float* src = which < 3 ? a.prep + (t * 3 + which) * n + h * d + c
+                                         : a.proj + t * a.ld + (which == 3 ? a.off_k : a.off_r) + h * d + c;
+            dr_cp16(buf + (which * DR_TILE + tok) * d + c, src);
+        }
+    } else {
+        for (int e = tid; e < 5 * n_tok * d; e += nthr) {
+            int which = e / (n_tok * d), rem = e % (n_tok * d), tok = rem / d, c = rem % d;
+            size_t t = (size_t)(t0 + tok);
+            const float* src = which < 3 ? a.prep + (t * 3 + which) * n + h * d + c
+                                         : a.proj + t * a.ld + (which == 3 ? a.off_k : a.off_r) + h * d + c;
+            dr_cp4(buf + (which * DR_TILE + tok) * d + c, src);
+        }
+    }
+    for (int e = tid; e < n_tok * ncols; e += nthr) {
+        int tok = e / ncols, c = e % ncols;
+        dr_cp4(vbuf + tok * DR_COLS + c, a.proj + (size_t)(t0 + tok) * a.ld + a.off_v + h * d + col0 + c);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+}
+
+template <int RPT, bool VEC>
+__global__ void __launch_bounds__(DR_R * DR_COLS) delta_walk_kernel(DeltaArgs a) {
     ce_pdl_begin();
     extern __shared__ __align__(16) float dr_smem[];
-    int d = a.d, L = a.L, TT = a.tile;
-    float* kk = dr_smem;                 // [TT][d] keys
-    float* uu = kk + TT * d;             // unit keys
-    float* au = uu + TT * d;             // removal rate x unit key (the rate alone until the norm is known)
-    float* ww = au + TT * d;             // decays
-    float* rr = ww + TT * d;             // receptance
-    float* vv = rr + TT * d;             // values
-    float* gg = vv + TT * d;             // gate logits
-    float* oo = gg + TT * d;             // outputs before the norm
-    float* th = oo + TT * d;             // [TT][L] tanh of the narrow projection
-    float* red = th + TT * L;            // [TT] a per-token scalar
-
-    int h = blockIdx.x, b = blockIdx.y, tid = threadIdx.x, nthr = blockDim.x;
+    int d = a.d, n = a.H * d;
+    int h = blockIdx.x, b = blockIdx.y, col0 = blockIdx.z * DR_COLS, tid = threadIdx.x;
     int t_begin = a.q_start[b], t_end = a.q_start[b + 1];
     if (t_end <= t_begin) return;
-    int j = tid / DR_R, g = tid % DR_R;          // column of the state, and which rows of it
-    bool owner = j < d;
+    int ncols = min(DR_COLS, d - col0);
+    int jj = tid / DR_R, g = tid % DR_R, j = col0 + jj;
+    bool owner = jj < ncols;
     float* sp = a.state + ((size_t)a.seq_slot[b] * a.H + h) * d * d;
     float S[RPT];
 #pragma unroll
@@ -62,51 +150,26 @@ __global__ void __launch_bounds__(DR_R * DR_R * RPT) general_delta_kernel(DeltaA
         int i = g + DR_R * m;
         S[m] = (owner && i < d) ? sp[(size_t)i * d + j] : 0.f;
     }
-    int lane = tid & 31, warp = tid >> 5, nwarp = nthr >> 5;
-    const float decay_rate = 0.60653065971263342f;       // exp(-1/2)
-
-    for (int t0 = t_begin; t0 < t_end; t0 += TT) {
-        int n = min(TT, t_end - t0);
-        for (int e = tid; e < n * L; e += nthr) {
-            int tok = e / L, l = e % L;
-            th[e] = tanhf(a.proj[(size_t)(t0 + tok) * a.ld + a.off_z + l]);
+    int buf_floats = 5 * DR_TILE * d + DR_TILE * DR_COLS;
+    int n_tiles = (t_end - t_begin + DR_TILE - 1) / DR_TILE;
+    dr_stage<VEC>(a, dr_smem, t_begin, min(DR_TILE, t_end - t_begin), h, col0, ncols);
+    for (int tile = 0; tile < n_tiles; ++tile) {
+        int t0 = t_begin + tile * DR_TILE, n_tok = min(DR_TILE, t_end - t0);
+        float* buf = dr_smem + (tile & 1) * buf_floats;
+        if (tile + 1 < n_tiles) {
+            dr_stage<VEC>(a, dr_smem + ((tile + 1) & 1) * buf_floats, t0 + DR_TILE, min(DR_TILE, t_end - t0 - DR_TILE), h, col0, ncols);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
         }
         __syncthreads();
-        for (int e = tid; e < n * d; e += nthr) {
-            int tok = e / d, c = e % d, col = h * d + c;
-            const float* row = a.proj + (size_t)(t0 + tok) * a.ld;
-            float z = a.w0[col];
-            const float* w2r = a.w2 + (size_t)col * L;
-            const float* tr = th + tok * L;
-            for (int l = 0; l < L; ++l) z = fmaf(w2r[l], tr[l], z);
-            ww[e] = expf(-decay_rate * dr_sigmoid(z));
-            au[e] = dr_sigmoid(row[a.off_a + col] + a.a_bias[col]);
-            kk[e] = row[a.off_k + col];
-            rr[e] = row[a.off_r + col];
-            vv[e] = row[a.off_v + col];
-            gg[e] = row[a.off_g + col];
-        }
-        __syncthreads();
-        for (int tok = warp; tok < n; tok += nwarp) {        // sum of squares of each key: a warp per token
-            float ss = 0.f;
-            for (int c = lane; c < d; c += 32) ss = fmaf(kk[tok * d + c], kk[tok * d + c], ss);
-            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-            if (lane == 0) red[tok] = 1.0f / sqrtf(ss + 1e-6f);
-        }
-        __syncthreads();
-        for (int e = tid; e < n * d; e += nthr) {
-            float u = kk[e] * red[e / d];
-            uu[e] = u;
-            au[e] *= u;
-        }
-        __syncthreads();
-        // the walk: no barrier inside, every thread reads the prepared vectors and its own registers
-        for (int tok = 0; tok < n; ++tok) {
-            const float* u_ = uu + tok * d;
-            const float* au_ = au + tok * d;
-            const float* w_ = ww + tok * d;
-            const float* k_ = kk + tok * d;
-            const float* r_ = rr + tok * d;
+        const float* vbuf = buf + 5 * DR_TILE * d;
+        for (int tok = 0; tok < n_tok; ++tok) {
+            const float* w_ = buf + (0 * DR_TILE + tok) * d;
+            const float* u_ = buf + (1 * DR_TILE + tok) * d;
+            const float* au_ = buf + (2 * DR_TILE + tok) * d;
+            const float* k_ = buf + (3 * DR_TILE + tok) * d;
+            const float* r_ = buf + (4 * DR_TILE + tok) * d;
             float dot = 0.f;
 #pragma unroll
             for (int m = 0; m < RPT; ++m) {
@@ -115,7 +178,7 @@ __global__ void __launch_bounds__(DR_R * DR_R * RPT) general_delta_kernel(DeltaA
             }
 #pragma unroll
             for (int o = 1; o < DR_R; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-            float vj = owner ? vv[tok * d + j] : 0.f;
+            float vj = owner ? vbuf[tok * DR_COLS + jj] : 0.f;
             float out = 0.f;
 #pragma unroll
             for (int m = 0; m < RPT; ++m) {
@@ -128,22 +191,9 @@ __global__ void __launch_bounds__(DR_R * DR_R * RPT) general_delta_kernel(DeltaA
             }
 #pragma unroll
             for (int o = 1; o < DR_R; o <<= 1) out += __shfl_xor_sync(0xffffffffu, out, o);
-            if (owner && g == 0) oo[tok * d + j] = out;
+            if (owner && g == 0) a.raw[(size_t)(t0 + tok) * n + h * d + j] = out;
         }
-        __syncthreads();
-        for (int tok = warp; tok < n; tok += nwarp) {        // root mean square of each token's head output
-            float ss = 0.f;
-            for (int c = lane; c < d; c += 32) ss = fmaf(oo[tok * d + c], oo[tok * d + c], ss);
-            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-            if (lane == 0) red[tok] = 1.0f / sqrtf(ss / (float)d + a.eps);
-        }
-        __syncthreads();
-        for (int e = tid; e < n * d; e += nthr) {
-            int tok = e / d, c = e % d, col = h * d + c;
-            float y = oo[e] * red[tok] * a.norm_w[col] * dr_sigmoid(gg[e]);
-            CeType<T>::store((T*)a.out + (size_t)(t0 + tok) * a.H * d + col, y);
-        }
-        __syncthreads();
+        __syncthreads();             // the buffer is free for the tile after the next
     }
 #pragma unroll
     for (int m = 0; m < RPT; ++m) {
@@ -152,39 +202,66 @@ __global__ void __launch_bounds__(DR_R * DR_R * RPT) general_delta_kernel(DeltaA
     }
 }
 
-template <typename T, int RPT>
-static void launch_delta(const DeltaArgs& a, int B, size_t smem, cudaStream_t stream) {
-    int threads = (a.d * DR_R + 31) / 32 * 32;
-    if (smem > 48 * 1024)
-        cudaFuncSetAttribute(general_delta_kernel<T, RPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    ce_note("general_delta_kernel");
-    ce_launch(general_delta_kernel<T, RPT>, dim3(a.H, B), threads, smem, stream, a);
-}
-
+// One block per token, a warp per head in turn: root mean square over the head, weight, gate.
 template <typename T>
-static int dispatch_delta(const DeltaArgs& a, int B, size_t smem, cudaStream_t stream) {
-    int rpt = (a.d + DR_R - 1) / DR_R;
-    if (rpt <= 8) launch_delta<T, 8>(a, B, smem, stream);
-    else if (rpt <= 16) launch_delta<T, 16>(a, B, smem, stream);
-    else launch_delta<T, 32>(a, B, smem, stream);
-    return ce_check_launch("ce_general_delta");
+__global__ void delta_finish_kernel(DeltaArgs a) {
+    ce_pdl_begin();
+    int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    int d = a.d, n = a.H * d;
+    const float* o = a.raw + (size_t)t * n;
+    const float* row = a.proj + (size_t)t * a.ld;
+    for (int h = warp; h < a.H; h += nwarp) {
+        float ss = 0.f;
+        for (int c = lane; c < d; c += 32) ss = fmaf(o[h * d + c], o[h * d + c], ss);
+        for (int k = 16; k > 0; k >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, k);
+        float inv = 1.0f / sqrtf(ss / (float)d + a.eps);
+        for (int c = lane; c < d; c += 32) {
+            int col = h * d + c;
+            CeType<T>::store((T*)a.out + (size_t)t * n + col, o[col] * inv * a.norm_w[col] * dr_sigmoid(row[a.off_g + col]));
+        }
+    }
 }
 
-extern "C" int ce_general_delta(const float* proj, const float* w2, const float* w0, const float* a_bias,
-                                const float* norm_w, float* state, void* out, int out_dtype, const int* seq_slot,
-                                const int* q_start, int B, int ld, int off_r, int off_k, int off_v, int off_a, int off_g,
-                                int off_z, int H, int d, int L, float eps, cudaStream_t stream) {
-    if (B == 0) return CE_OK;
-    if (!proj || !w2 || !w0 || !a_bias || !norm_w || !state || !out || !seq_slot || !q_start)
+template <int RPT>
+static void launch_walk(const DeltaArgs& a, int B, bool vec, cudaStream_t stream) {
+    size_t smem = (size_t)2 * (5 * DR_TILE * a.d + DR_TILE * DR_COLS) * sizeof(float);
+    dim3 grid(a.H, B, (a.d + DR_COLS - 1) / DR_COLS);
+    ce_note("delta_walk_kernel");
+    if (vec) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(delta_walk_kernel<RPT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        ce_launch(delta_walk_kernel<RPT, true>, grid, DR_R * DR_COLS, smem, stream, a);
+    } else {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(delta_walk_kernel<RPT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        ce_launch(delta_walk_kernel<RPT, false>, grid, DR_R * DR_COLS, smem, stream, a);
+    }
+}
+
+// proj [T, ld] float32 with r, k, v, a, g at their offsets; zz [T, H*d] the decay logits; prep [T, 3*H*d] and raw
+// [T, H*d] float32 work space; state [slots, H, d, d]; out [T, H*d] in out_dtype.
+extern "C" int ce_general_delta(const float* proj, const float* zz, const float* w0, const float* a_bias, const float* norm_w,
+                                float* prep, float* raw, float* state, void* out, int out_dtype, const int* seq_slot,
+                                const int* q_start, int T, int B, int ld, int off_r, int off_k, int off_v, int off_a, int off_g,
+                                int H, int d, float eps, cudaStream_t stream) {
+    if (B == 0 || T == 0) return CE_OK;
+    if (!proj || !zz || !w0 || !a_bias || !norm_w || !prep || !raw || !state || !out || !seq_slot || !q_start)
         return ce_fail(CE_ERR_ARG, "ce_general_delta: null pointer");
-    if (d <= 0 || d > 128) return ce_fail(CE_ERR_SIZE, "ce_general_delta: head size %d not in 1..128", d);
-    if (H <= 0 || L <= 0 || B > 65535) return ce_fail(CE_ERR_SIZE, "ce_general_delta: %d heads, rank %d, %d sequences", H, L, B);
-    int tile = d <= 64 ? 16 : d <= 128 ? 8 : 4;
-    DeltaArgs a{proj, w2, w0, a_bias, norm_w, state, out, seq_slot, q_start, ld, off_r, off_k, off_v, off_a, off_g, off_z,
-                H, d, L, tile, eps};
-    size_t smem = (size_t)(8 * tile * d + tile * L + tile) * sizeof(float);
-    if (smem > 200 * 1024) return ce_fail(CE_ERR_SIZE, "ce_general_delta: rank %d is too large", L);
-    if (out_dtype == CE_F32) return dispatch_delta<float>(a, B, smem, stream);
-    if (out_dtype == CE_BF16) return dispatch_delta<__nv_bfloat16>(a, B, smem, stream);
-    return ce_fail(CE_ERR_ARG, "ce_general_delta: unknown dtype %d", out_dtype);
+    if (d <= 0 || d > 256) return ce_fail(CE_ERR_SIZE, "ce_general_delta: head size %d not in 1..256", d);
+    if (H <= 0 || B > 65535) return ce_fail(CE_ERR_SIZE, "ce_general_delta: %d heads, %d sequences", H, B);
+    if (out_dtype != CE_F32 && out_dtype != CE_BF16) return ce_fail(CE_ERR_ARG, "ce_general_delta: unknown dtype %d", out_dtype);
+    DeltaArgs a{proj, zz, w0, a_bias, norm_w, prep, raw, state, out, seq_slot, q_start, ld, off_r, off_k, off_v, off_a, off_g, H, d, eps};
+    int threads = H >= 8 ? 256 : 32 * H;
+    ce_note("delta_prepare_kernel");
+    ce_launch(delta_prepare_kernel, T, threads, 0, stream, a);
+    // 16-byte copies where every source address is a multiple of 16: all of the row stride, the offsets and d
+    bool vec = d % 4 == 0 && ld % 4 == 0 && off_k % 4 == 0 && off_r % 4 == 0 &&
+               (((uintptr_t)proj | (uintptr_t)prep) & 15) == 0;
+    int rpt = (d + DR_R - 1) / DR_R;
+    if (rpt <= 4) launch_walk<4>(a, B, vec, stream);
+    else if (rpt <= 8) launch_walk<8>(a, B, vec, stream);
+    else if (rpt <= 16) launch_walk<16>(a, B, vec, stream);
+    else launch_walk<32>(a, B, vec, stream);
+    ce_note("delta_finish_kernel");
+    if (out_dtype == CE_F32) ce_launch(delta_finish_kernel<float>, T, threads, 0, stream, a);
+    else ce_launch(delta_finish_kernel<__nv_bfloat16>, T, threads, 0, stream, a);
+    return ce_check_launch("ce_general_delta");
 }

@@ -1,0 +1,287 @@
+// Differential attention for portions of prompts in bfloat16 on the tensor cores (mma.sync m16n8k16),
+// over the paged cache.  The float32 kernel of diff_attention.cu is its plain twin.
+//
+// One block per (tile of 64 query tokens of one sequence, query head), eight warps: warps 0..3 compute
+// map 1 for 16 query rows each, warps 4..7 map 2 for the same rows.  Each warp is a flash attention of its
+// own (S = Q K^T in float32, online softmax, P rounded to bfloat16, O += P V in float32) over tiles of 64
+// keys; both maps read the same V tile and their own K tile.  At the end the warps of map 2 hand their
+// normalised rows over through shared memory and the warps of map 1 finish the head:
+// o = a1 - lambda a2, unit root mean square over the head times out_scale, times sigmoid(gate), one store.
+//
+// Visible keys per row: causal, optionally the last ``window``, optionally only the row's own block of
+// ``chunk`` positions; a tile of queries may straddle blocks, so the mask is applied per element.
+#include "common.cuh"
+
+#define FA_BM 64
+#define FA_BN 64
+#define FA_THREADS 256
+#define FA_PAD 8                 // bf16 elements of padding per shared-memory row (16 bytes: conflict-free ldmatrix)
+
+struct FlashDiffArgs {
+    const __nv_bfloat16* q;      // [T, q_stride]; head h: map 1 at column h*2*d, map 2 at h*2*d + d
+    const __nv_bfloat16* k_pool; // [pages, 2 nkv, page, d]
+    const __nv_bfloat16* v_pool; // [pages, nkv, page, dv]
+    const __nv_bfloat16* gate;   // [T, gate_stride] or null
+    __nv_bfloat16* out;          // [T, nh*dv]
+    const int* positions;
+    const int* seq_slot;
+    const int* q_start;
+    const int* block_table;
+    const int* tiles;            // (sequence, first token of the tile within the sequence's tokens of the step)
+    int* status;
+    int nh, nkv, d, dv, q_stride, gate_stride, page_size, max_pages, num_pages, window, chunk;
+    float scale, lambda, eps, out_scale;
+};
+
+__device__ __forceinline__ void fa_ldmatrix_x4(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const void* p) {
+    unsigned s = (unsigned)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(s));
+}
+__device__ __forceinline__ void fa_ldmatrix_x4_trans(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const void* p) {
+    unsigned s = (unsigned)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(s));
+}
+__device__ __forceinline__ void fa_mma(float* c, const unsigned* a, unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned fa_pack(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<unsigned*>(&v);
+}
+
+// DK: 16-element steps of a map the registers hold (d <= 16 DK); DVT: 8-column tiles of a value head (dv <= 8 DVT)
+template <int DK, int DVT>
+__global__ void __launch_bounds__(FA_THREADS) diff_attention_mma_kernel(FlashDiffArgs a) {
+    ce_pdl_begin();
+    extern __shared__ __align__(16) unsigned char fa_smem[];
+    const int d = a.d, dv = a.dv, ldk = d + FA_PAD, ldv = dv + FA_PAD;
+    __nv_bfloat16* Qs = (__nv_bfloat16*)fa_smem;             // [2][64][ldk]
+    __nv_bfloat16* Ks = Qs + 2 * FA_BM * ldk;                // [2][64][ldk]
+    __nv_bfloat16* Vs = Ks + 2 * FA_BN * ldk;                // [64][ldv]
+    float* comb = (float*)(Vs + FA_BN * ldv);                // [64][dv] map 2's rows
+    __shared__ int s_pos[FA_BM];
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int map = warp >> 2, row0 = (warp & 3) * 16;
+    const int b = a.tiles[2 * blockIdx.x], q0 = a.tiles[2 * blockIdx.x + 1], h = blockIdx.y;
+    const int kvh = h / (a.nh / a.nkv);
+    const int t0 = a.q_start[b] + q0, n_rows = min(FA_BM, a.q_start[b + 1] - t0);
+    const int* table = a.block_table + (size_t)a.seq_slot[b] * a.max_pages;
+
+    if (tid < FA_BM) s_pos[tid] = tid < n_rows ? a.positions[t0 + tid] : -1;
+    // the queries of both maps
+    const int c8 = d >> 3;
+    for (int e = tid; e < 2 * FA_BM * c8; e += FA_THREADS) {
+        int m = e / (FA_BM * c8), r = (e / c8) % FA_BM, c = (e % c8) * 8;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (r < n_rows) v = *reinterpret_cast<const uint4*>(a.q + (size_t)(t0 + r) * a.q_stride + (size_t)h * 2 * d + m * d + c);
+        *reinterpret_cast<uint4*>(Qs + (m * FA_BM + r) * ldk + c) = v;
+    }
+    __syncthreads();
+    const int pos_first = s_pos[0], pos_last = s_pos[n_rows - 1];
+    int lo_blk = a.window > 0 ? max(0, pos_first - a.window + 1) : 0;
+    if (a.chunk > 0) lo_blk = max(lo_blk, pos_first / a.chunk * a.chunk);
+    // this thread's two rows
+    const int ra = row0 + (lane >> 2), rb = ra + 8;
+    const int pos_a = s_pos[ra], pos_b = s_pos[rb];
+    int lo_a = a.window > 0 ? max(0, pos_a - a.window + 1) : 0, lo_b = a.window > 0 ? max(0, pos_b - a.window + 1) : 0;
+    if (a.chunk > 0 && pos_a >= 0) lo_a = max(lo_a, pos_a / a.chunk * a.chunk);
+    if (a.chunk > 0 && pos_b >= 0) lo_b = max(lo_b, pos_b / a.chunk * a.chunk);
+
+    unsigned qf[DK][4];
+#pragma unroll
+    for (int ks = 0; ks < DK; ++ks)
+        if (ks * 16 < d)
+            fa_ldmatrix_x4(qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3],
+                           Qs + (map * FA_BM + row0 + (lane & 15)) * ldk + ks * 16 + (lane >> 4) * 8);
+    float o[DVT][4];
+#pragma unroll
+    for (int i = 0; i < DVT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
+    const float LOG2E = 1.4426950408889634f;
+    const int v8 = dv >> 3;
+
+    for (int k0 = lo_blk / FA_BN * FA_BN; k0 <= pos_last; k0 += FA_BN) {
+        // K of both maps and V, from the pages; rows past the last visible key are zeros
+        for (int e = tid; e < 2 * FA_BN * c8; e += FA_THREADS) {
+            int m = e / (FA_BN * c8), r = (e / c8) % FA_BN, c = (e % c8) * 8;
+            int key = k0 + r;
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (key <= pos_last) {
+                int page = table[key / a.page_size];
+                if (page < 0 || page >= a.num_pages) atomicExch(a.status, 4);
+                else v = *reinterpret_cast<const uint4*>(
+                        a.k_pool + (((size_t)page * 2 * a.nkv + 2 * kvh + m) * a.page_size + key % a.page_size) * d + c);
+            }
+            *reinterpret_cast<uint4*>(Ks + (m * FA_BN + r) * ldk + c) = v;
+        }
+        for (int e = tid; e < FA_BN * v8; e += FA_THREADS) {
+            int r = e / v8, c = (e % v8) * 8;
+            int key = k0 + r;
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (key <= pos_last) {
+                int page = table[key / a.page_size];
+                if (page >= 0 && page < a.num_pages)
+                    v = *reinterpret_cast<const uint4*>(
+                        a.v_pool + (((size_t)page * a.nkv + kvh) * a.page_size + key % a.page_size) * dv + c);
+            }
+            *reinterpret_cast<uint4*>(Vs + r * ldv + c) = v;
+        }
+        __syncthreads();
+
+        float s[FA_BN / 8][4];
+#pragma unroll
+        for (int i = 0; i < FA_BN / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+        const __nv_bfloat16* Km = Ks + map * FA_BN * ldk;
+#pragma unroll
+        for (int ks = 0; ks < DK; ++ks) {
+            if (ks * 16 < d) {
+#pragma unroll
+                for (int nt = 0; nt < FA_BN / 8; nt += 2) {
+                    unsigned b0, b1, b2, b3;
+                    fa_ldmatrix_x4(b0, b1, b2, b3, Km + (nt * 8 + (lane >> 4) * 8 + (lane & 7)) * ldk + ks * 16 + ((lane >> 3) & 1) * 8);
+                    fa_mma(s[nt], qf[ks], b0, b1);
+                    fa_mma(s[nt + 1], qf[ks], b2, b3);
+                }
+            }
+        }
+        // scale, mask, running maximum
+        float mx_a = -INFINITY, mx_b = -INFINITY;
+#pragma unroll
+        for (int nt = 0; nt < FA_BN / 8; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                int key = k0 + nt * 8 + (lane & 3) * 2 + (e & 1);
+                bool upper = e < 2;
+                bool see = upper ? (key <= pos_a && key >= lo_a) : (key <= pos_b && key >= lo_b);
+                float v = see ? s[nt][e] * a.scale : -INFINITY;
+                s[nt][e] = v;
+                if (upper) mx_a = fmaxf(mx_a, v); else mx_b = fmaxf(mx_b, v);
+            }
+        }
+        mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1)); mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
+        mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1)); mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
+        float n_a = fmaxf(m_a, mx_a), n_b = fmaxf(m_b, mx_b);
+        float use_a = n_a == -INFINITY ? 0.f : n_a, use_b = n_b == -INFINITY ? 0.f : n_b;
+        float f_a = m_a == -INFINITY ? 0.f : ce_exp2_fast((m_a - use_a) * LOG2E);
+        float f_b = m_b == -INFINITY ? 0.f : ce_exp2_fast((m_b - use_b) * LOG2E);
+        m_a = n_a; m_b = n_b;
+        float sum_a = 0.f, sum_b = 0.f;
+        unsigned pf[FA_BN / 16][4];
+#pragma unroll
+        for (int nt = 0; nt < FA_BN / 8; ++nt) {
+            float p0 = ce_exp2_fast((s[nt][0] - use_a) * LOG2E), p1 = ce_exp2_fast((s[nt][1] - use_a) * LOG2E);
+            float p2 = ce_exp2_fast((s[nt][2] - use_b) * LOG2E), p3 = ce_exp2_fast((s[nt][3] - use_b) * LOG2E);
+            sum_a += p0 + p1;
+            sum_b += p2 + p3;
+            pf[nt >> 1][(nt & 1) * 2] = fa_pack(p0, p1);
+            pf[nt >> 1][(nt & 1) * 2 + 1] = fa_pack(p2, p3);
+        }
+        sum_a += __shfl_xor_sync(0xffffffffu, sum_a, 1); sum_a += __shfl_xor_sync(0xffffffffu, sum_a, 2);
+        sum_b += __shfl_xor_sync(0xffffffffu, sum_b, 1); sum_b += __shfl_xor_sync(0xffffffffu, sum_b, 2);
+        l_a = l_a * f_a + sum_a;
+        l_b = l_b * f_b + sum_b;
+#pragma unroll
+        for (int i = 0; i < DVT; ++i) { o[i][0] *= f_a; o[i][1] *= f_a; o[i][2] *= f_b; o[i][3] *= f_b; }
+        // O += P V
+#pragma unroll
+        for (int kk = 0; kk < FA_BN / 16; ++kk) {
+#pragma unroll
+            for (int nt = 0; nt < DVT; nt += 2) {
+                if (nt * 8 < dv) {
+                    unsigned b0, b1, b2, b3;
+                    fa_ldmatrix_x4_trans(b0, b1, b2, b3, Vs + (kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * ldv + nt * 8 + (lane >> 4) * 8);
+                    fa_mma(o[nt], pf[kk], b0, b1);
+                    fa_mma(o[nt + 1], pf[kk], b2, b3);
+                }
+            }
+        }
+        __syncthreads();
+    }
+    float i_a = l_a > 0.f ? 1.0f / l_a : 0.f, i_b = l_b > 0.f ? 1.0f / l_b : 0.f;
+    const int cq = (lane & 3) * 2;
+    if (map == 1) {
+#pragma unroll
+        for (int nt = 0; nt < DVT; ++nt) {
+            if (nt * 8 < dv) {
+                *reinterpret_cast<float2*>(comb + ra * dv + nt * 8 + cq) = make_float2(o[nt][0] * i_a, o[nt][1] * i_a);
+                *reinterpret_cast<float2*>(comb + rb * dv + nt * 8 + cq) = make_float2(o[nt][2] * i_b, o[nt][3] * i_b);
+            }
+        }
+    }
+    __syncthreads();
+    if (map == 0) {
+        float ss_a = 0.f, ss_b = 0.f;
+#pragma unroll
+        for (int nt = 0; nt < DVT; ++nt) {
+            if (nt * 8 < dv) {
+                float2 xa = *reinterpret_cast<const float2*>(comb + ra * dv + nt * 8 + cq);
+                float2 xb = *reinterpret_cast<const float2*>(comb + rb * dv + nt * 8 + cq);
+                o[nt][0] = o[nt][0] * i_a - a.lambda * xa.x; o[nt][1] = o[nt][1] * i_a - a.lambda * xa.y;
+                o[nt][2] = o[nt][2] * i_b - a.lambda * xb.x; o[nt][3] = o[nt][3] * i_b - a.lambda * xb.y;
+                ss_a += o[nt][0] * o[nt][0] + o[nt][1] * o[nt][1];
+                ss_b += o[nt][2] * o[nt][2] + o[nt][3] * o[nt][3];
+            }
+        }
+        ss_a += __shfl_xor_sync(0xffffffffu, ss_a, 1); ss_a += __shfl_xor_sync(0xffffffffu, ss_a, 2);
+        ss_b += __shfl_xor_sync(0xffffffffu, ss_b, 1); ss_b += __shfl_xor_sync(0xffffffffu, ss_b, 2);
+        float g_a = 1.f, g_b = 1.f;
+        if (a.gate) {
+            if (ra < n_rows) g_a = 1.0f / (1.0f + expf(-__bfloat162float(a.gate[(size_t)(t0 + ra) * a.gate_stride + h])));
+            if (rb < n_rows) g_b = 1.0f / (1.0f + expf(-__bfloat162float(a.gate[(size_t)(t0 + rb) * a.gate_stride + h])));
+        }
+        float mul_a = a.out_scale * g_a / sqrtf(ss_a / (float)dv + a.eps), mul_b = a.out_scale * g_b / sqrtf(ss_b / (float)dv + a.eps);
+#pragma unroll
+        for (int nt = 0; nt < DVT; ++nt) {
+            if (nt * 8 < dv) {
+                if (ra < n_rows)
+                    *reinterpret_cast<unsigned*>(a.out + ((size_t)(t0 + ra) * a.nh + h) * dv + nt * 8 + cq) = fa_pack(o[nt][0] * mul_a, o[nt][1] * mul_a);
+                if (rb < n_rows)
+                    *reinterpret_cast<unsigned*>(a.out + ((size_t)(t0 + rb) * a.nh + h) * dv + nt * 8 + cq) = fa_pack(o[nt][2] * mul_b, o[nt][3] * mul_b);
+            }
+        }
+    }
+}
+
+extern "C" int ce_diff_attention_mma_supported(int d, int dv, int q_stride) {
+    return d >= 16 && d <= 128 && d % 16 == 0 && dv >= 16 && dv <= 256 && dv % 16 == 0 && q_stride % 8 == 0;
+}
+
+template <int DK, int DVT>
+static void launch_flash_diff(const FlashDiffArgs& a, int n_tiles, cudaStream_t stream) {
+    size_t smem = (size_t)(4 * FA_BM * (a.d + FA_PAD) + FA_BN * (a.dv + FA_PAD)) * sizeof(__nv_bfloat16) + (size_t)FA_BM * a.dv * sizeof(float);
+    if (smem > 48 * 1024)
+        cudaFuncSetAttribute(diff_attention_mma_kernel<DK, DVT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    ce_note("diff_attention_mma_kernel");
+    ce_launch(diff_attention_mma_kernel<DK, DVT>, dim3(n_tiles, a.nh), FA_THREADS, smem, stream, a);
+}
+
+extern "C" int ce_diff_attention_mma(const void* q, const void* k_pool, const void* v_pool, const void* gate, void* out,
+                                     const int* positions, const int* seq_slot, const int* q_start, const int* block_table,
+                                     const int* tiles, int* status, int n_tiles, int nh, int nkv, int d, int dv, int q_stride,
+                                     int gate_stride, int page_size, int max_pages, int num_pages, int window, int chunk,
+                                     float scale, float lambda, float eps, float out_scale, cudaStream_t stream) {
+    if (n_tiles == 0) return CE_OK;
+    if (!q || !k_pool || !v_pool || !out || !positions || !seq_slot || !q_start || !block_table || !tiles || !status)
+        return ce_fail(CE_ERR_ARG, "ce_diff_attention_mma: null pointer");
+    if (!ce_diff_attention_mma_supported(d, dv, q_stride))
+        return ce_fail(CE_ERR_SIZE, "ce_diff_attention_mma: head sizes %d / %d or row stride %d not supported", d, dv, q_stride);
+    if (nkv <= 0 || nh % nkv != 0)
+        return ce_fail(CE_ERR_SIZE, "ce_diff_attention_mma: %d heads are not a multiple of %d kv heads", nh, nkv);
+    if ((((uintptr_t)q | (uintptr_t)k_pool | (uintptr_t)v_pool) & 15) || (((uintptr_t)out) & 3))
+        return ce_fail(CE_ERR_SIZE, "ce_diff_attention_mma: operands must be 16-byte aligned");
+    FlashDiffArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, (const __nv_bfloat16*)gate,
+                    (__nv_bfloat16*)out, positions, seq_slot, q_start, block_table, tiles, status, nh, nkv, d, dv, q_stride,
+                    gate_stride, page_size, max_pages, num_pages, window, chunk, scale, lambda, eps, out_scale};
+    if (d <= 64) {
+        if (dv <= 64) launch_flash_diff<4, 8>(a, n_tiles, stream);
+        else if (dv <= 128) launch_flash_diff<4, 16>(a, n_tiles, stream);
+        else launch_flash_diff<4, 32>(a, n_tiles, stream);
+    } else {
+        if (dv <= 64) launch_flash_diff<8, 8>(a, n_tiles, stream);
+        else if (dv <= 128) launch_flash_diff<8, 16>(a, n_tiles, stream);
+        else launch_flash_diff<8, 32>(a, n_tiles, stream);
+    }
+    return ce_check_launch("ce_diff_attention_mma");
+}

@@ -333,9 +333,12 @@ class ModelRunner:
         key = (ctx.B,) + tuple(getattr(ctx.plans[k], "graph_key", None) for k in self._planners)
         entry = self._graphs.get(key)
         if entry is None:
-            # once eagerly, so that lazy initialisation (library handles, kernel attributes) is not captured
+            # This step runs eagerly, and its results are the step's (lazy initialisation of library handles and
+            # kernel attributes happens here, outside the capture).  The capture that follows records the launches
+            # without running them, so the step is applied ONCE: a mixer with a recurrent state would otherwise
+            # advance twice.
             x = self.model.forward(ctx, self.storage)
-            self.model.logits(ctx, x, rows)
+            eager_logits = self.model.logits(ctx, x, rows)
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
             before = ops.launch_count()
@@ -344,8 +347,9 @@ class ModelRunner:
                 logits = self.model.logits(ctx, x, rows)
             if self._graph_pool is None:
                 self._graph_pool = graph.pool()
-            entry = (graph, logits, ops.launch_count() - before)
-            self._graphs[key] = entry
+            self._graphs[key] = (graph, logits, ops.launch_count() - before)
+            ops.add_launches(before - ops.launch_count())        # the captured launches did not run
+            return eager_logits
         graph, logits, launches = entry
         graph.replay()
         ops.add_launches(launches)

@@ -368,8 +368,8 @@ def bias_rope_kvwrite(qkv, k_pool, v_pool, bias, cos, sin, positions, seq_of_tok
 
 def diff_attention(q, q_stride: int, k_pool, v_pool, gate, gate_stride: int, out, positions, seq_of_token, seq_slot,
                    block_table, status, nh: int, nkv: int, d: int, dv: int, page_size: int, window: int, chunk: int,
-                   scale: float, lam: float, eps: float, out_scale: float) -> None:
-    """Differential attention in float32 arithmetic: two softmax maps per head over the same values,
+                   scale: float, lam: float, eps: float, out_scale: float, n_tokens: Optional[int] = None) -> None:
+    """Differential attention in float32 arithmetic (``n_tokens``: only the first so many tokens of the step): two softmax maps per head over the same values,
     o = a1 - lam a2, unit RMS per head times ``out_scale``, times sigmoid(gate logit)."""
     _need(k_pool, "k_pool"); _need(v_pool, "v_pool", k_pool.dtype); _need(out, "out", k_pool.dtype)
     if q.dtype != k_pool.dtype:
@@ -383,20 +383,54 @@ def diff_attention(q, q_stride: int, k_pool, v_pool, gate, gate_stride: int, out
         float(eps), float(out_scale), _stream()))
 
 
-def general_delta(proj, w2, w0, a_bias, norm_w, state, out, seq_slot, q_start, n_seqs: int, offsets: Sequence[int],
-                  heads: int, d: int, rank: int, eps: float) -> None:
+def diff_attention_mma_supported(d: int, dv: int, q_stride: int) -> bool:
+    return bool(kernels().ce_diff_attention_mma_supported(d, dv, q_stride))
+
+
+def diff_attention_mma(q, q_stride: int, k_pool, v_pool, gate, gate_stride: int, out, positions, seq_slot, q_start,
+                       block_table, tiles, n_tiles: int, status, nh: int, nkv: int, d: int, dv: int, page_size: int,
+                       window: int, chunk: int, scale: float, lam: float, eps: float, out_scale: float) -> None:
+    """Differential attention on the tensor cores (bfloat16) for tiles of 64 query tokens: ``tiles`` holds
+    (sequence, first token within the sequence's tokens of the step) pairs."""
+    _need(k_pool, "k_pool", torch.bfloat16); _need(v_pool, "v_pool", torch.bfloat16); _need(out, "out", torch.bfloat16)
+    if q.dtype != torch.bfloat16:
+        raise KernelError("diff_attention_mma: bfloat16 only")
+    if k_pool.shape[1] != 2 * nkv or k_pool.shape[3] != d or v_pool.shape[1] != nkv or v_pool.shape[3] != dv:
+        raise KernelError(f"diff_attention_mma: pools {tuple(k_pool.shape)} / {tuple(v_pool.shape)} do not fit {nkv} key heads")
+    _ok(kernels().ce_diff_attention_mma(
+        _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(gate), _ptr(out), _ptr(positions), _ptr(seq_slot), _ptr(q_start),
+        _ptr(block_table), _ptr(tiles), _ptr(status), int(n_tiles), nh, nkv, d, dv, q_stride, gate_stride, page_size,
+        block_table.shape[1], k_pool.shape[0], int(window), int(chunk), float(scale), float(lam), float(eps),
+        float(out_scale), _stream()))
+
+
+def tanh_cols(proj: torch.Tensor, off: int, width: int, out: torch.Tensor) -> None:
+    """out[t, l] = tanh(proj[t, off + l]) for l < width; proj float32, out float32 or bfloat16 [T, width]."""
+    _need(proj, "proj", torch.float32); _need(out, "out")
+    if out.shape != (proj.shape[0], width) or off + width > proj.shape[1]:
+        raise KernelError("tanh_cols: sizes do not fit")
+    _ok(kernels().ce_tanh_cols(_ptr(proj), _ptr(out), dtype_code(out.dtype), proj.shape[0], proj.stride(0), int(off),
+                               int(width), _stream()))
+
+
+def general_delta(proj, zz, w0, a_bias, norm_w, prep, raw, state, out, seq_slot, q_start, n_seqs: int,
+                  offsets: Sequence[int], heads: int, d: int, eps: float) -> None:
     """The generalized delta rule over each sequence's tokens of the step, from and to ``state``
-    [slots, heads, d, d] (float32).  ``proj`` float32 [T, ld] holds, at ``offsets`` (r, k, v, a, g, z), the
-    projections of every token; ``out`` [T, heads * d] receives the normed, gated outputs."""
+    [slots, heads, d, d] (float32).  ``proj`` float32 [T, ld] holds, at ``offsets`` (r, k, v, a, g), the
+    projections of every token, ``zz`` [T, heads * d] the decay logits; ``prep`` [T, 3 * heads * d] and ``raw``
+    [T, heads * d] are float32 work space; ``out`` [T, heads * d] receives the normed, gated outputs.  Three
+    launches: prepare, walk, finish."""
     _need(proj, "proj", torch.float32); _need(state, "state", torch.float32); _need(out, "out")
-    for name, t in (("w2", w2), ("w0", w0), ("a_bias", a_bias), ("norm_w", norm_w)):
+    for name, t in (("zz", zz), ("w0", w0), ("a_bias", a_bias), ("norm_w", norm_w), ("prep", prep), ("raw", raw)):
         _need(t, name, torch.float32)
-    if tuple(state.shape[1:]) != (heads, d, d) or out.shape[1] != heads * d or w2.shape != (heads * d, rank):
+    T, n = out.shape[0], heads * d
+    if tuple(state.shape[1:]) != (heads, d, d) or out.shape[1] != n or zz.shape != (T, n) or prep.numel() < 3 * T * n \
+            or raw.numel() < T * n:
         raise KernelError("general_delta: sizes do not fit")
-    off_r, off_k, off_v, off_a, off_g, off_z = (int(o) for o in offsets)
-    _ok(kernels().ce_general_delta(_ptr(proj), _ptr(w2), _ptr(w0), _ptr(a_bias), _ptr(norm_w), _ptr(state), _ptr(out),
-                                   dtype_code(out.dtype), _ptr(seq_slot), _ptr(q_start), n_seqs, proj.stride(0), off_r, off_k,
-                                   off_v, off_a, off_g, off_z, heads, d, rank, float(eps), _stream()))
+    off_r, off_k, off_v, off_a, off_g = (int(o) for o in offsets)
+    _ok(kernels().ce_general_delta(_ptr(proj), _ptr(zz), _ptr(w0), _ptr(a_bias), _ptr(norm_w), _ptr(prep), _ptr(raw),
+                                   _ptr(state), _ptr(out), dtype_code(out.dtype), _ptr(seq_slot), _ptr(q_start), T, n_seqs,
+                                   proj.stride(0), off_r, off_k, off_v, off_a, off_g, heads, d, float(eps), _stream()), 3)
 
 
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:

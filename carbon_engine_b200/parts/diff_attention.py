@@ -22,6 +22,7 @@ from typing import List, Optional
 import torch
 
 from .. import ops
+from .attention import PagedAttention
 from .base import Mixer, PagedCacheSpec, Part, TensorGetter, TensorSpec, register_init_kind
 from .linear import ACCUM, STORE, STORE_F32, Linear
 from .rope import PositionEncoding
@@ -32,6 +33,11 @@ register_init_kind("lambda_vec", 0.0, 0.1, True)
 class DifferentialAttention(Mixer):
     graph_safe = True
     can_store = True
+    # the step's tiles of query tokens are those of the paged attention: one plan serves every attention layer
+    plan_key = PagedAttention.plan_key
+    TILE, TILE_TC = PagedAttention.TILE, PagedAttention.TILE_TC
+    step_sections = PagedAttention.step_sections
+    plan_step = PagedAttention.plan_step
 
     def __init__(self, hidden: int, heads: int, kv_heads: int, dim: int, vdim: int, prefix: str, diff: float, eps: float,
                  position: Optional[PositionEncoding] = None, scale: Optional[float] = None, chunk: int = 0,
@@ -98,6 +104,18 @@ class DifferentialAttention(Mixer):
                 keys += before + n
                 pairs += n * before + n * (n + 1) // 2      # an upper bound: chunks and windows see fewer
             prof.note_work((keys * G * (2 * d + dv) + ctx.T * H * (2 * d + dv)) * el, 4 * pairs * H * (d + dv))
-        ops.diff_attention(qkvg, qkvg.stride(0), cache.k_pool, cache.v_pool, gate, qkvg.stride(0), out, ctx.positions,
-                           ctx.seq_of_token, ctx.seq_slot, table, ctx.status, H, G, d, dv, cache.page_size, self.window,
-                           self.chunk, self.scale, self.lam, self.eps, 1.0 - self.diff)
+        consts = (self.window, self.chunk, self.scale, self.lam, self.eps, 1.0 - self.diff)
+        stride = qkvg.stride(0)
+        n_plain = ctx.T
+        if qkvg.dtype == torch.bfloat16 and ctx.fast_attention and ops.diff_attention_mma_supported(d, dv, stride):
+            # portions of prompts on the tensor cores, a tile of 64 query tokens a block; the one-token sequences
+            # (they come first in a step) on the float32 kernel, whose block is one (token, head)
+            plan = ctx.plans[self.plan_key]
+            if plan.n_tiles > 0:
+                ops.diff_attention_mma(qkvg, stride, cache.k_pool, cache.v_pool, gate, stride, out, ctx.positions, ctx.seq_slot,
+                                       ctx.q_start, table, plan.tiles, plan.n_tiles, ctx.status, H, G, d, dv, cache.page_size,
+                                       *consts)
+            n_plain = ctx.n_decode
+        if n_plain > 0:
+            ops.diff_attention(qkvg, stride, cache.k_pool, cache.v_pool, gate, stride, out, ctx.positions, ctx.seq_of_token,
+                               ctx.seq_slot, table, ctx.status, H, G, d, dv, cache.page_size, *consts, n_tokens=n_plain)
