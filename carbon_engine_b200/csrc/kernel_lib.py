@@ -43,8 +43,8 @@ _SIGNATURES = {
     "ce_scatter_i32": (_i, [_p, _p, _p, _i, _ll, _p]),
     # x, coef, w, out, out_dtype, rows, R, S, W, groups, eps, stream
     "ce_streams_norm": (_i, [_p, _p, _p, _p, _i, _p, _i, _i, _i, _i, _f, _p]),
-    # h, mu, state, out, out_dtype, positions, seq_of_token, seq_slot, q_start, T, W, stream
-    "ce_token_shift": (_i, [_p, _p, _p, _p, _i, _p, _p, _p, _p, _i, _i, _p]),
+    # h, mu, state, out, out_dtype, positions, seq_of_token, seq_slot, q_start, T, W, save, stream
+    "ce_token_shift": (_i, [_p, _p, _p, _p, _i, _p, _p, _p, _p, _i, _i, _i, _p]),
     # h, state, seq_slot, q_start, B, W, stream
     "ce_save_last_rows": (_i, [_p, _p, _p, _p, _i, _i, _p]),
     # x, y, mix, c_out, bias, T, S, W, stream
@@ -66,8 +66,8 @@ _SIGNATURES = {
     # proj, out, out_dtype, T, ld, off, L, stream
     "ce_tanh_cols": (_i, [_p, _p, _i, _i, _i, _i, _i, _p]),
     # proj, zz, w0, a_bias, norm_w, prep, raw, state, out, out_dtype, seq_slot, q_start, T, B, ld, off_r, off_k, off_v,
-    # off_a, off_g, H, d, eps, stream
-    "ce_general_delta": (_i, [_p] * 9 + [_i] + [_p] * 2 + [_i] * 10 + [_f, _p]),
+    # off_a, off_g, H, d, eps, stage, stream
+    "ce_general_delta": (_i, [_p] * 9 + [_i] + [_p] * 2 + [_i] * 10 + [_f, _i, _p]),
 }
 
 

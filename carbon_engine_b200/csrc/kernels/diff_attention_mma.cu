@@ -8,6 +8,9 @@
 // normalised rows over through shared memory and the warps of map 1 finish the head:
 // o = a1 - lambda a2, unit root mean square over the head times out_scale, times sigmoid(gate), one store.
 //
+// K and V tiles come from the pages by cp.async into two buffers, a tile ahead of the arithmetic; the page of
+// every key row of a tile is looked up two tiles ahead, so that no copy waits for a table entry.
+//
 // Visible keys per row: causal, optionally the last ``window``, optionally only the row's own block of
 // ``chunk`` positions; a tile of queries may straddle blocks, so the mask is applied per element.
 #include "common.cuh"
@@ -57,10 +60,11 @@ __global__ void __launch_bounds__(FA_THREADS) diff_attention_mma_kernel(FlashDif
     extern __shared__ __align__(16) unsigned char fa_smem[];
     const int d = a.d, dv = a.dv, ldk = d + FA_PAD, ldv = dv + FA_PAD;
     __nv_bfloat16* Qs = (__nv_bfloat16*)fa_smem;             // [2][64][ldk]
-    __nv_bfloat16* Ks = Qs + 2 * FA_BM * ldk;                // [2][64][ldk]
-    __nv_bfloat16* Vs = Ks + 2 * FA_BN * ldk;                // [64][ldv]
-    float* comb = (float*)(Vs + FA_BN * ldv);                // [64][dv] map 2's rows
+    __nv_bfloat16* stage0 = Qs + 2 * FA_BM * ldk;            // two buffers of K [2][64][ldk] and V [64][ldv]
+    const int stage_elems = 2 * FA_BN * ldk + FA_BN * ldv;
+    float* comb = (float*)stage0;                            // [64][dv] map 2's rows, once the key tiles are done
     __shared__ int s_pos[FA_BM];
+    __shared__ int s_page[2][FA_BN];                         // page of every key row of the tile a buffer will hold
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int map = warp >> 2, row0 = (warp & 3) * 16;
@@ -100,35 +104,82 @@ __global__ void __launch_bounds__(FA_THREADS) diff_attention_mma_kernel(FlashDif
     for (int i = 0; i < DVT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
     const float LOG2E = 1.4426950408889634f;
-    const int v8 = dv >> 3;
 
-    for (int k0 = lo_blk / FA_BN * FA_BN; k0 <= pos_last; k0 += FA_BN) {
-        // K of both maps and V, from the pages; rows past the last visible key are zeros
-        for (int e = tid; e < 2 * FA_BN * c8; e += FA_THREADS) {
-            int m = e / (FA_BN * c8), r = (e / c8) % FA_BN, c = (e % c8) * 8;
-            int key = k0 + r;
-            uint4 v = make_uint4(0u, 0u, 0u, 0u);
-            if (key <= pos_last) {
-                int page = table[key / a.page_size];
-                if (page < 0 || page >= a.num_pages) atomicExch(a.status, 4);
-                else v = *reinterpret_cast<const uint4*>(
-                        a.k_pool + (((size_t)page * 2 * a.nkv + 2 * kvh + m) * a.page_size + key % a.page_size) * d + c);
+    // the page of key row r of the tile at k0, or -1 (no such key, or a page the request does not hold)
+    auto page_of = [&](int k0, int r) -> int {
+        int key = k0 + r;
+        if (key > pos_last) return -1;
+        int page = table[key / a.page_size];
+        if (page < 0 || page >= a.num_pages) { atomicExch(a.status, 4); return -1; }
+        return page;
+    };
+    // copies of the tile at k0 into buffer ``which``, whose rows' pages are in s_page[which]
+    auto stage = [&](int k0, int which) {
+        __nv_bfloat16* Kd = stage0 + which * stage_elems;
+        __nv_bfloat16* Vd = Kd + 2 * FA_BN * ldk;
+        const int* pages = s_page[which];
+        {   // K: two threads a row of the 2 x 64 rows (map, key), each every second 16-byte piece
+            int row = tid >> 1, m = row >> 6, r = row & (FA_BN - 1);
+            __nv_bfloat16* dst = Kd + row * ldk;
+            int page = pages[r];
+            if (page >= 0) {
+                const __nv_bfloat16* src = a.k_pool + (((size_t)page * 2 * a.nkv + 2 * kvh + m) * a.page_size + (k0 + r) % a.page_size) * d;
+                for (int c = (tid & 1) * 8; c < d; c += 16) {
+                    unsigned sa = (unsigned)__cvta_generic_to_shared(dst + c);
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sa), "l"(src + c));
+                }
+            } else {
+                for (int c = (tid & 1) * 8; c < d; c += 16) *reinterpret_cast<uint4*>(dst + c) = make_uint4(0u, 0u, 0u, 0u);
             }
-            *reinterpret_cast<uint4*>(Ks + (m * FA_BN + r) * ldk + c) = v;
         }
-        for (int e = tid; e < FA_BN * v8; e += FA_THREADS) {
-            int r = e / v8, c = (e % v8) * 8;
-            int key = k0 + r;
-            uint4 v = make_uint4(0u, 0u, 0u, 0u);
-            if (key <= pos_last) {
-                int page = table[key / a.page_size];
-                if (page >= 0 && page < a.num_pages)
-                    v = *reinterpret_cast<const uint4*>(
-                        a.v_pool + (((size_t)page * a.nkv + kvh) * a.page_size + key % a.page_size) * dv + c);
+        {   // V: four threads a row, each every fourth piece
+            int r = tid >> 2;
+            __nv_bfloat16* dst = Vd + r * ldv;
+            int page = pages[r];
+            if (page >= 0) {
+                const __nv_bfloat16* src = a.v_pool + (((size_t)page * a.nkv + kvh) * a.page_size + (k0 + r) % a.page_size) * dv;
+                for (int c = (tid & 3) * 8; c < dv; c += 32) {
+                    unsigned sa = (unsigned)__cvta_generic_to_shared(dst + c);
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sa), "l"(src + c));
+                }
+            } else {
+                for (int c = (tid & 3) * 8; c < dv; c += 32) *reinterpret_cast<uint4*>(dst + c) = make_uint4(0u, 0u, 0u, 0u);
             }
-            *reinterpret_cast<uint4*>(Vs + r * ldv + c) = v;
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    // a tile of keys that every row of this warp sees whole needs no mask: all 16 rows are tokens, the tile ends at or
+    // before the first row's position and begins at or after the last row's first visible key
+    const bool rows_full = row0 + 15 < n_rows;
+    const int warp_pos_first = s_pos[row0];
+    int warp_lo_last = 0;
+    if (rows_full) {
+        int pl = s_pos[row0 + 15];
+        warp_lo_last = a.window > 0 ? max(0, pl - a.window + 1) : 0;
+        if (a.chunk > 0) warp_lo_last = max(warp_lo_last, pl / a.chunk * a.chunk);
+    }
+    const int k_first = lo_blk / FA_BN * FA_BN;
+    if (tid < FA_BN) {
+        s_page[0][tid] = page_of(k_first, tid);
+        s_page[1][tid] = page_of(k_first + FA_BN, tid);
+    }
+    __syncthreads();
+    stage(k_first, 0);
+    int it = 0;
+    for (int k0 = k_first; k0 <= pos_last; k0 += FA_BN, ++it) {
+        const int cur = it & 1;
+        const bool more = k0 + FA_BN <= pos_last;
+        int page_ahead = -1;                        // for the tile after the next: asked for now, stored after the arithmetic
+        if (tid < FA_BN && more) page_ahead = page_of(k0 + 2 * FA_BN, tid);
+        if (more) {
+            stage(k0 + FA_BN, cur ^ 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
         }
         __syncthreads();
+        const __nv_bfloat16* Ks = stage0 + cur * stage_elems;
+        const __nv_bfloat16* Vs = Ks + 2 * FA_BN * ldk;
 
         float s[FA_BN / 8][4];
 #pragma unroll
@@ -148,16 +199,25 @@ __global__ void __launch_bounds__(FA_THREADS) diff_attention_mma_kernel(FlashDif
         }
         // scale, mask, running maximum
         float mx_a = -INFINITY, mx_b = -INFINITY;
+        if (rows_full && k0 + FA_BN - 1 <= warp_pos_first && k0 >= warp_lo_last) {
 #pragma unroll
-        for (int nt = 0; nt < FA_BN / 8; ++nt) {
+            for (int nt = 0; nt < FA_BN / 8; ++nt) {
+                s[nt][0] *= a.scale; s[nt][1] *= a.scale; s[nt][2] *= a.scale; s[nt][3] *= a.scale;
+                mx_a = fmaxf(mx_a, fmaxf(s[nt][0], s[nt][1]));
+                mx_b = fmaxf(mx_b, fmaxf(s[nt][2], s[nt][3]));
+            }
+        } else {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                int key = k0 + nt * 8 + (lane & 3) * 2 + (e & 1);
-                bool upper = e < 2;
-                bool see = upper ? (key <= pos_a && key >= lo_a) : (key <= pos_b && key >= lo_b);
-                float v = see ? s[nt][e] * a.scale : -INFINITY;
-                s[nt][e] = v;
-                if (upper) mx_a = fmaxf(mx_a, v); else mx_b = fmaxf(mx_b, v);
+            for (int nt = 0; nt < FA_BN / 8; ++nt) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    int key = k0 + nt * 8 + (lane & 3) * 2 + (e & 1);
+                    bool upper = e < 2;
+                    bool see = upper ? (key <= pos_a && key >= lo_a) : (key <= pos_b && key >= lo_b);
+                    float v = see ? s[nt][e] * a.scale : -INFINITY;
+                    s[nt][e] = v;
+                    if (upper) mx_a = fmaxf(mx_a, v); else mx_b = fmaxf(mx_b, v);
+                }
             }
         }
         mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1)); mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
@@ -197,6 +257,7 @@ __global__ void __launch_bounds__(FA_THREADS) diff_attention_mma_kernel(FlashDif
                 }
             }
         }
+        if (tid < FA_BN) s_page[cur][tid] = page_ahead;      // buffer ``cur`` will hold the tile after the next
         __syncthreads();
     }
     float i_a = l_a > 0.f ? 1.0f / l_a : 0.f, i_b = l_b > 0.f ? 1.0f / l_b : 0.f;
@@ -250,7 +311,7 @@ extern "C" int ce_diff_attention_mma_supported(int d, int dv, int q_stride) {
 
 template <int DK, int DVT>
 static void launch_flash_diff(const FlashDiffArgs& a, int n_tiles, cudaStream_t stream) {
-    size_t smem = (size_t)(4 * FA_BM * (a.d + FA_PAD) + FA_BN * (a.dv + FA_PAD)) * sizeof(__nv_bfloat16) + (size_t)FA_BM * a.dv * sizeof(float);
+    size_t smem = (size_t)(2 * FA_BM * (a.d + FA_PAD) + 2 * (2 * FA_BN * (a.d + FA_PAD) + FA_BN * (a.dv + FA_PAD))) * sizeof(__nv_bfloat16);
     if (smem > 48 * 1024)
         cudaFuncSetAttribute(diff_attention_mma_kernel<DK, DVT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     ce_note("diff_attention_mma_kernel");

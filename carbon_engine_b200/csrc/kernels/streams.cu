@@ -48,6 +48,84 @@ __global__ void streams_norm_kernel(const float* __restrict__ x, const float* __
     }
 }
 
+// The same for widths and groups that are multiples of four: float4 loads of every stream, float4 through shared
+// memory, four outputs a store.
+__device__ __forceinline__ void st_store4(float* p, float a, float b, float c, float d) {
+    *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+}
+__device__ __forceinline__ void st_store4(__nv_bfloat16* p, float a, float b, float c, float d) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    uint2 r;
+    r.x = *reinterpret_cast<unsigned*>(&lo); r.y = *reinterpret_cast<unsigned*>(&hi);
+    *reinterpret_cast<uint2*>(p) = r;
+}
+
+template <typename T, int SMAX>
+__global__ void streams_norm_vec_kernel(const float* __restrict__ x, const float* __restrict__ coef,
+                                        const float* __restrict__ w, T* __restrict__ out, const int* __restrict__ rows,
+                                        int S, int W, int groups, float eps) {
+    ce_pdl_begin();
+    extern __shared__ __align__(16) float st_smem[];
+    float4* u4 = reinterpret_cast<float4*>(st_smem);        // W / 4
+    float* scratch = st_smem + W;                           // 32
+    int r = blockIdx.x, n4 = W >> 2;
+    const float4* xr = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * S * W);
+    float c[SMAX];
+#pragma unroll
+    for (int s = 0; s < SMAX; ++s) c[s] = s < S ? (coef ? coef[s] : 1.0f) : 0.f;
+    for (int j = threadIdx.x; j < n4; j += blockDim.x) {
+        float4 v[SMAX];
+#pragma unroll
+        for (int s = 0; s < SMAX; ++s)
+            if (s < S) v[s] = xr[(size_t)s * n4 + j];
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int s = 0; s < SMAX; ++s)
+            if (s < S) { acc.x = fmaf(c[s], v[s].x, acc.x); acc.y = fmaf(c[s], v[s].y, acc.y); acc.z = fmaf(c[s], v[s].z, acc.z); acc.w = fmaf(c[s], v[s].w, acc.w); }
+        u4[j] = acc;
+    }
+    __syncthreads();
+    int g4 = n4 / groups;
+    const float4* w4 = reinterpret_cast<const float4*>(w);
+    T* o = out + (size_t)r * W;
+    for (int g = 0; g < groups; ++g) {
+        const float4* ug = u4 + g * g4;
+        float ss = 0.f;
+        for (int j = threadIdx.x; j < g4; j += blockDim.x) {
+            float4 v = ug[j];
+            ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+        }
+        ss = ce_block_sum(ss, scratch);
+        float inv = 1.0f / sqrtf(ss / (float)(4 * g4) + eps);
+        for (int j = threadIdx.x; j < g4; j += blockDim.x) {
+            float4 v = ug[j], wv = w4[g * g4 + j];
+            st_store4(o + 4 * (g * g4 + j), v.x * inv * wv.x, v.y * inv * wv.y, v.z * inv * wv.z, v.w * inv * wv.w);
+        }
+    }
+}
+
+template <typename T>
+static void launch_streams_norm(const float* x, const float* coef, const float* w, T* out, const int* rows, int R, int S, int W,
+                                int groups, float eps, size_t smem, cudaStream_t stream) {
+    bool vec = W % 4 == 0 && (W / groups) % 4 == 0 && ((((uintptr_t)x | (uintptr_t)w | (uintptr_t)out)) & 15) == 0 && S <= 8;
+    if (vec) {
+        int threads = W >= 4096 ? 512 : W >= 1024 ? 256 : 128;
+        ce_note("streams_norm_vec_kernel");
+        if (S <= 4) {
+            if (smem > 48 * 1024) cudaFuncSetAttribute(streams_norm_vec_kernel<T, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            ce_launch(streams_norm_vec_kernel<T, 4>, R, threads, smem, stream, x, coef, w, out, rows, S, W, groups, eps);
+        } else {
+            if (smem > 48 * 1024) cudaFuncSetAttribute(streams_norm_vec_kernel<T, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            ce_launch(streams_norm_vec_kernel<T, 8>, R, threads, smem, stream, x, coef, w, out, rows, S, W, groups, eps);
+        }
+        return;
+    }
+    int threads = W / groups >= 1024 ? 512 : 256;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(streams_norm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    ce_note("streams_norm_kernel");
+    ce_launch(streams_norm_kernel<T>, R, threads, smem, stream, x, coef, w, out, rows, S, W, groups, eps);
+}
+
 extern "C" int ce_streams_norm(const float* x, const float* coef, const float* w, void* out, int out_dtype,
                                const int* rows, int R, int S, int W, int groups, float eps, cudaStream_t stream) {
     if (R == 0) return CE_OK;
@@ -56,57 +134,61 @@ extern "C" int ce_streams_norm(const float* x, const float* coef, const float* w
     if (W <= 0 || groups <= 0 || W % groups) return ce_fail(CE_ERR_SIZE, "ce_streams_norm: width %d in %d groups", W, groups);
     size_t smem = (size_t)(W + 32) * sizeof(float);
     if (smem > 200 * 1024) return ce_fail(CE_ERR_SIZE, "ce_streams_norm: width %d is too large", W);
-    int threads = W / groups >= 1024 ? 512 : 256;
-    if (out_dtype == CE_F32) {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(streams_norm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        ce_note("streams_norm_kernel");
-        ce_launch(streams_norm_kernel<float>, R, threads, smem, stream, x, coef, w, (float*)out, rows, S, W, groups, eps);
-    } else if (out_dtype == CE_BF16) {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(streams_norm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        ce_note("streams_norm_kernel");
-        ce_launch(streams_norm_kernel<__nv_bfloat16>, R, threads, smem, stream, x, coef, w, (__nv_bfloat16*)out, rows, S, W, groups, eps);
-    } else
-        return ce_fail(CE_ERR_ARG, "ce_streams_norm: unknown dtype %d", out_dtype);
+    if (out_dtype == CE_F32) launch_streams_norm<float>(x, coef, w, (float*)out, rows, R, S, W, groups, eps, smem, stream);
+    else if (out_dtype == CE_BF16) launch_streams_norm<__nv_bfloat16>(x, coef, w, (__nv_bfloat16*)out, rows, R, S, W, groups, eps, smem, stream);
+    else return ce_fail(CE_ERR_ARG, "ce_streams_norm: unknown dtype %d", out_dtype);
     return ce_check_launch("ce_streams_norm");
 }
 
 // ---------------------------------------------------------------------------------------------
 // Token shift: out[t] = h[t] + (prev(t) - h[t]) * mu, where prev(t) is the row of the token before t
 // in its sequence as it was before the shift: h[t - 1] inside the step, the row kept in
-// state[slot] for the first token of a portion, zeros at position 0.
+// state[slot] for the first token of a portion, zeros at position 0.  With ``save`` the kept row becomes the
+// portion's last row (written by the block that read the old one, so the two never race).
 // ---------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void token_shift_kernel(const float* __restrict__ h, const float* __restrict__ mu,
-                                   const float* __restrict__ state, T* __restrict__ out,
+                                   float* __restrict__ state, T* __restrict__ out,
                                    const int* __restrict__ positions, const int* __restrict__ seq_of_token,
-                                   const int* __restrict__ seq_slot, const int* __restrict__ q_start, int W) {
+                                   const int* __restrict__ seq_slot, const int* __restrict__ q_start, int W, int save) {
     ce_pdl_begin();
     int t = blockIdx.x;
     int b = seq_of_token[t];
-    const float* prev = nullptr;
-    if (t > q_start[b]) prev = h + (size_t)(t - 1) * W;
-    else if (positions[t] > 0) prev = state + (size_t)seq_slot[b] * W;
     const float* hr = h + (size_t)t * W;
     T* o = out + (size_t)t * W;
+    if (t > q_start[b]) {
+        const float* prev = h + (size_t)(t - 1) * W;
+        for (int j = threadIdx.x; j < W; j += blockDim.x) {
+            float v = hr[j];
+            CeType<T>::store(o + j, fmaf(prev[j] - v, mu[j], v));
+        }
+        return;
+    }
+    // The first token of the sequence's portion: the only block that touches the sequence's kept row.  Each
+    // thread reads its elements of the row and then (save) puts the portion's last row in their place.
+    float* kept = state + (size_t)seq_slot[b] * W;
+    const float* last = h + (size_t)(q_start[b + 1] - 1) * W;
+    bool first = positions[t] == 0;
     for (int j = threadIdx.x; j < W; j += blockDim.x) {
-        float v = hr[j], p = prev ? prev[j] : 0.f;
+        float v = hr[j], p = first ? 0.f : kept[j];
         CeType<T>::store(o + j, fmaf(p - v, mu[j], v));
+        if (save) kept[j] = last[j];
     }
 }
 
-extern "C" int ce_token_shift(const float* h, const float* mu, const float* state, void* out, int out_dtype,
+extern "C" int ce_token_shift(const float* h, const float* mu, float* state, void* out, int out_dtype,
                               const int* positions, const int* seq_of_token, const int* seq_slot, const int* q_start,
-                              int T, int W, cudaStream_t stream) {
+                              int T, int W, int save, cudaStream_t stream) {
     if (T == 0) return CE_OK;
     if (!h || !mu || !state || !out || !positions || !seq_of_token || !seq_slot || !q_start)
         return ce_fail(CE_ERR_ARG, "ce_token_shift: null pointer");
     int threads = W >= 1024 ? 256 : 128;
     if (out_dtype == CE_F32) {
         ce_note("token_shift_kernel");
-        ce_launch(token_shift_kernel<float>, T, threads, 0, stream, h, mu, state, (float*)out, positions, seq_of_token, seq_slot, q_start, W);
+        ce_launch(token_shift_kernel<float>, T, threads, 0, stream, h, mu, state, (float*)out, positions, seq_of_token, seq_slot, q_start, W, save);
     } else if (out_dtype == CE_BF16) {
         ce_note("token_shift_kernel");
-        ce_launch(token_shift_kernel<__nv_bfloat16>, T, threads, 0, stream, h, mu, state, (__nv_bfloat16*)out, positions, seq_of_token, seq_slot, q_start, W);
+        ce_launch(token_shift_kernel<__nv_bfloat16>, T, threads, 0, stream, h, mu, state, (__nv_bfloat16*)out, positions, seq_of_token, seq_slot, q_start, W, save);
     } else
         return ce_fail(CE_ERR_ARG, "ce_token_shift: unknown dtype %d", out_dtype);
     return ce_check_launch("ce_token_shift");

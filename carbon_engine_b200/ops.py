@@ -292,15 +292,15 @@ def streams_norm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: 
 
 
 def token_shift(h: torch.Tensor, mu: torch.Tensor, state: torch.Tensor, out: torch.Tensor, positions, seq_of_token,
-                seq_slot, q_start) -> None:
+                seq_slot, q_start, save: bool = True) -> None:
     """out[t] = h[t] + (previous row - h[t]) * mu; the previous row of a portion's first token is state[slot]
-    (zeros at position 0).  h and state float32."""
+    (zeros at position 0).  h and state float32.  ``save``: state[slot] then becomes the portion's last row."""
     _need(h, "h", torch.float32); _need(mu, "mu", torch.float32); _need(state, "state", torch.float32); _need(out, "out")
     T, W = h.shape
     if out.shape != h.shape or mu.numel() != W or state.shape[-1] != W:
         raise KernelError("token_shift: sizes differ")
     _ok(kernels().ce_token_shift(_ptr(h), _ptr(mu), _ptr(state), _ptr(out), dtype_code(out.dtype), _ptr(positions),
-                                 _ptr(seq_of_token), _ptr(seq_slot), _ptr(q_start), T, W, _stream()))
+                                 _ptr(seq_of_token), _ptr(seq_slot), _ptr(q_start), T, W, 1 if save else 0, _stream()))
 
 
 def save_last_rows(h: torch.Tensor, state: torch.Tensor, seq_slot: torch.Tensor, q_start: torch.Tensor) -> None:
@@ -428,9 +428,15 @@ def general_delta(proj, zz, w0, a_bias, norm_w, prep, raw, state, out, seq_slot,
             or raw.numel() < T * n:
         raise KernelError("general_delta: sizes do not fit")
     off_r, off_k, off_v, off_a, off_g = (int(o) for o in offsets)
-    _ok(kernels().ce_general_delta(_ptr(proj), _ptr(zz), _ptr(w0), _ptr(a_bias), _ptr(norm_w), _ptr(prep), _ptr(raw),
-                                   _ptr(state), _ptr(out), dtype_code(out.dtype), _ptr(seq_slot), _ptr(q_start), T, n_seqs,
-                                   proj.stride(0), off_r, off_k, off_v, off_a, off_g, heads, d, float(eps), _stream()), 3)
+    prof, work = profiling(), None
+    if prof is not None:
+        work, prof._work = prof._work, (0, 0)            # the caller's figures belong to the walk
+    for stage in (1, 2, 3):
+        if stage == 2 and work is not None:
+            prof.note_work(*work)
+        _ok(kernels().ce_general_delta(_ptr(proj), _ptr(zz), _ptr(w0), _ptr(a_bias), _ptr(norm_w), _ptr(prep), _ptr(raw),
+                                       _ptr(state), _ptr(out), dtype_code(out.dtype), _ptr(seq_slot), _ptr(q_start), T, n_seqs,
+                                       proj.stride(0), off_r, off_k, off_v, off_a, off_g, heads, d, float(eps), stage, _stream()))
 
 
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:

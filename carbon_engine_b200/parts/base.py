@@ -154,7 +154,9 @@ class Mixer(Part):
 
         Parts that can also STORE their result (float32, into a buffer that holds nothing yet) take a keyword
         ``accumulate=False`` and say so with ``can_store = True``: blocks whose residual is not a plain
-        sum (several streams) ask for that."""
+        sum (several streams) ask for that.  With ``accumulate=False`` a part may return a float32 bias [width]
+        that the caller still has to add to what was stored (it is then added in the kernel that reads the
+        output next); None: nothing is owed."""
         raise NotImplementedError
 
 

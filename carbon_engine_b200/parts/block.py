@@ -83,8 +83,8 @@ class StreamBlock(Block):
             self.mixer.forward(ctx, h, x, cache)
         else:
             y = ctx.buffer((T, W), torch.float32)
-            self.mixer.forward(ctx, h, y, cache, accumulate=False)
-            hc[0].write(x, y)
+            owed = self.mixer.forward(ctx, h, y, cache, accumulate=False)
+            hc[0].write(x, y, owed)
         # the feed-forward
         if self.ffn is None:
             return
@@ -92,5 +92,5 @@ class StreamBlock(Block):
         if hc is None:
             self.ffn.forward(ctx, h, x)
         else:
-            self.ffn.forward(ctx, h, y, accumulate=False)
-            hc[1].write(x, y)
+            owed = self.ffn.forward(ctx, h, y, accumulate=False)
+            hc[1].write(x, y, owed)

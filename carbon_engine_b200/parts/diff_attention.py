@@ -91,7 +91,9 @@ class DifferentialAttention(Mixer):
                               pos.rotary_dim if cos is not None else 0, cache.page_size, write_kv=cache.writes)
         out = ctx.buffer((T, H * dv))
         self.attend(ctx, qkvg, out, cache, table)
-        self.o.forward(out, x, ACCUM if accumulate else STORE_F32)
+        # stored, not added: the output bias is left to the caller, whose next kernel reads the output anyway
+        self.o.forward(out, x, ACCUM if accumulate else STORE_F32, add_bias=accumulate)
+        return None if accumulate else self.o.bias
 
     def attend(self, ctx, qkvg: torch.Tensor, out: torch.Tensor, cache, table: torch.Tensor) -> None:
         H, G, d, dv = self.heads, self.kv_heads, self.dim, self.vdim

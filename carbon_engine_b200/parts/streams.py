@@ -39,8 +39,9 @@ class HyperConnection(Part):
         f32 = lambda n: get(f"{self.prefix}.{n}").to(device).to(torch.float32).contiguous()
         self.c_in, self.c_out, self.mix = f32("in"), f32("out"), f32("mix")
 
-    def write(self, x: torch.Tensor, y: torch.Tensor) -> None:
-        ops.streams_write(x, y, self.mix, self.c_out)
+    def write(self, x: torch.Tensor, y: torch.Tensor, bias: Optional[torch.Tensor] = None) -> None:
+        """``bias`` (float32 [width]): added to ``y`` on the way, for a sublayer that left its output bias to its caller."""
+        ops.streams_write(x, y, self.mix, self.c_out, bias)
 
 
 class TokenShift(Part):
@@ -60,5 +61,4 @@ class TokenShift(Part):
     def forward(self, ctx, h: torch.Tensor, out: torch.Tensor, state: torch.Tensor) -> None:
         """``h`` float32 [T, width] (the rows before the blend), ``out`` what the mixer reads, ``state``
         [slots, width]: read for the first token of every portion, then given every sequence's last row."""
-        ops.token_shift(h, self.mu, state, out, ctx.positions, ctx.seq_of_token, ctx.seq_slot, ctx.q_start)
-        ops.save_last_rows(h, state, ctx.seq_slot, ctx.q_start)
+        ops.token_shift(h, self.mu, state, out, ctx.positions, ctx.seq_of_token, ctx.seq_slot, ctx.q_start, save=True)

@@ -60,6 +60,31 @@ def test_streams_write_and_broadcast_kernels():
         assert rel_err(xd.cpu().numpy(), want.numpy()) < 1e-5
 
 
+def test_token_shift_kernel_over_two_steps():
+    """Two sequences in two steps (one of them a single token in the second): the first token of every portion
+    takes the row the step before left in the slot's state, zeros at position 0."""
+    from carbon_engine_b200 import ops
+    g = torch.Generator().manual_seed(3)
+    W = 40
+    mu = torch.rand(W, generator=g)
+    seqs = [torch.randn(7, W, generator=g), torch.randn(4, W, generator=g)]
+    want = [plain.token_shift(s.double(), mu.double()).numpy() for s in seqs]
+    state = torch.full((3, W), float("nan"), device="cuda")
+    slots = torch.tensor([2, 0], dtype=torch.int32, device="cuda")
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
+    got = [[], []]
+    for cut0, cut1 in (((0, 5), (0, 3)), ((5, 7), (3, 4))):
+        h = torch.cat([seqs[0][cut0[0]:cut0[1]], seqs[1][cut1[0]:cut1[1]]]).cuda()
+        n0, n1 = cut0[1] - cut0[0], cut1[1] - cut1[0]
+        out = torch.empty_like(h)
+        ops.token_shift(h, mu.cuda(), state, out, i32(list(range(cut0[0], cut0[1])) + list(range(cut1[0], cut1[1]))),
+                        i32([0] * n0 + [1] * n1), slots, i32([0, n0, n0 + n1]))
+        got[0].append(out[:n0].cpu()); got[1].append(out[n0:].cpu())
+    for b in range(2):
+        assert rel_err(torch.cat(got[b]).numpy(), want[b]) < 1e-6
+    assert torch.equal(state[2].cpu(), seqs[0][-1]) and torch.equal(state[0].cpu(), seqs[1][-1])
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", sorted(SINGLE))
 def test_one_layer_of_each_kind(tmp_path, name, dtype):
