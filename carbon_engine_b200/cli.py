@@ -112,18 +112,35 @@ def cmd_tiny_model(a) -> int:
     from . import models  # noqa: F401
     from .config.qwen3 import Qwen3Config
     from .weights.loader import write_random_model
-    if a.arch != "qwen3":
-        raise SystemExit(f"--arch {a.arch}: only qwen3 is built")
+    if a.arch not in ("qwen3", "munizen"):
+        raise SystemExit(f"--arch {a.arch}: qwen3 and munizen are built")
     heads = a.heads or 4
     head_dim = a.head_dim or 16
+    store = {"f32": torch.float32, "bf16": torch.bfloat16}.get(a.dtype)
+    if store is None:
+        raise SystemExit("--dtype must be f32 or bf16")
+    if a.arch == "munizen":
+        # layers alternate between the recurrent mixer (no feed-forward) and differential attention (with one);
+        # a map of a head is half of --head-dim, a value head is --head-dim
+        from .config.munizen import MunizenConfig
+        kv = a.kv_heads or max(1, heads // 2)
+        attn = {"type": "attention", "mlp": {"kind": "dense", "ff": a.intermediate or 2 * a.hidden},
+                "mixer": {"heads": heads, "kv_heads": kv, "dim": max(2, head_dim // 2), "vdim": head_dim, "diff": 0.3,
+                          "scale": (max(2, head_dim // 2)) ** -0.5, "rot": {"dims": max(2, head_dim // 4 * 2), "base": a.rope_theta},
+                          "mask": {"size": a.mask_size}}}
+        delta = {"type": "general_delta", "mlp": None,
+                 "mixer": {"heads": max(1, a.hidden // head_dim), "dim": head_dim, "rank": max(4, a.hidden // 16)}}
+        cfg = MunizenConfig.from_dict({"architecture": "Munizen", "vocab": a.vocab, "width": a.hidden,
+                                       "layers": [delta if i % 2 == 0 else attn for i in range(a.layers)],
+                                       "norm": {"eps": a.rms_norm_eps, "groups": 2 if a.hidden % 2 == 0 else 1},
+                                       "streams": a.streams if a.streams > 0 else None, "max_position_embeddings": a.max_positions})
+        print(f"wrote {write_random_model(cfg, a.out, seed=a.seed, store_dtype=store)}")
+        return 0
     cfg = Qwen3Config.from_dict(dict(
         architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=a.layers, hidden_size=a.hidden,
         num_attention_heads=heads, num_key_value_heads=a.kv_heads or max(1, heads // 2), head_dim=head_dim,
         intermediate_size=a.intermediate or 2 * a.hidden, vocab_size=a.vocab, rope_theta=a.rope_theta,
         rms_norm_eps=a.rms_norm_eps, tie_word_embeddings=a.tie_word_embeddings, max_position_embeddings=a.max_positions))
-    store = {"f32": torch.float32, "bf16": torch.bfloat16}.get(a.dtype)
-    if store is None:
-        raise SystemExit("--dtype must be f32 or bf16")
     out = write_random_model(cfg, a.out, seed=a.seed, store_dtype=store)
     print(f"wrote {out}")
     return 0
@@ -163,7 +180,9 @@ def main(argv: Optional[List[str]] = None) -> int:
 
     t = sub.add_parser("tiny-model", help="write a small random model folder")
     t.add_argument("--out", required=True)
-    t.add_argument("--arch", default="qwen3")
+    t.add_argument("--arch", default="qwen3", help="qwen3 | munizen")
+    t.add_argument("--streams", type=int, default=2, help="munizen: residual streams (0: an ordinary residual)")
+    t.add_argument("--mask-size", type=int, default=256, help="munizen: positions in a block of the attention mask")
     t.add_argument("--layers", type=int, default=4)
     t.add_argument("--hidden", type=int, default=64)
     t.add_argument("--heads", type=int, default=None)

@@ -23,7 +23,7 @@
 // instructions a warp spends per token: sixteen lanes a column leave each thread four to sixteen rows.
 #include "common.cuh"
 
-#define DR_R 16                  // lanes that share a column of the state
+#define DR_R 16                  // lanes that share a column of the state (the walk's exchanges are written for 16)
 #define DR_COLS 8                // value channels a block walks
 #define DR_TILE 16               // tokens a buffer holds (at most DR_R: lane g of a column stores token g's output)
 
@@ -194,8 +194,16 @@ __global__ void __launch_bounds__(DR_R * DR_COLS) delta_walk_kernel(DeltaArgs a)
                     p2 = fmaf(u.z, S[4 * m + 2], p2); p3 = fmaf(u.w, S[4 * m + 3], p3);
                 }
                 float dot = (p0 + p1) + (p2 + p3);
-#pragma unroll
-                for (int o = 1; o < DR_R; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+                // over the column's sixteen lanes in two rounds of four: the three exchanges of a round are in flight
+                // together, and every lane adds the same pairs, so all sixteen hold the same sum
+                {
+                    float e1 = __shfl_xor_sync(0xffffffffu, dot, 1), e2 = __shfl_xor_sync(0xffffffffu, dot, 2),
+                          e3 = __shfl_xor_sync(0xffffffffu, dot, 3);
+                    dot = (dot + e1) + (e2 + e3);
+                    float f1 = __shfl_xor_sync(0xffffffffu, dot, 4), f2 = __shfl_xor_sync(0xffffffffu, dot, 8),
+                          f3 = __shfl_xor_sync(0xffffffffu, dot, 12);
+                    dot = (dot + f1) + (f2 + f3);
+                }
                 float vj = owner ? vbuf[tok * DR_COLS + jj] : 0.f;
                 float q0 = 0.f, q1 = 0.f, q2 = 0.f, q3 = 0.f;
 #pragma unroll

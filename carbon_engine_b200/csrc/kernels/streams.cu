@@ -250,6 +250,47 @@ __global__ void streams_write_kernel(float* __restrict__ x, const float* __restr
     }
 }
 
+// The same, four columns a thread (width a multiple of four, 16-byte aligned rows).
+template <int SMAX>
+__global__ void streams_write_vec_kernel(float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ mix,
+                                         const float* __restrict__ c_out, const float* __restrict__ bias, int S, int W4,
+                                         size_t total4) {
+    ce_pdl_begin();
+    __shared__ float m[SMAX * SMAX], co[SMAX];
+    for (int i = threadIdx.x; i < S * S; i += blockDim.x) m[i] = mix[i];
+    for (int i = threadIdx.x; i < S; i += blockDim.x) co[i] = c_out[i];
+    __syncthreads();
+    size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total4; e += stride) {
+        size_t t = e / W4;
+        int j = (int)(e % W4);
+        float4* xr = reinterpret_cast<float4*>(x) + t * S * W4 + j;
+        float4 old[SMAX];
+#pragma unroll
+        for (int s = 0; s < SMAX; ++s)
+            if (s < S) old[s] = xr[(size_t)s * W4];
+        float4 yv = reinterpret_cast<const float4*>(y)[e];
+        if (bias) {
+            float4 b = reinterpret_cast<const float4*>(bias)[j];
+            yv.x += b.x; yv.y += b.y; yv.z += b.z; yv.w += b.w;
+        }
+#pragma unroll
+        for (int to = 0; to < SMAX; ++to) {
+            if (to < S) {
+                float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int s = 0; s < SMAX; ++s)
+                    if (s < S) {
+                        float c = m[s * S + to];
+                        a.x = fmaf(c, old[s].x, a.x); a.y = fmaf(c, old[s].y, a.y); a.z = fmaf(c, old[s].z, a.z); a.w = fmaf(c, old[s].w, a.w);
+                    }
+                float c = co[to];
+                xr[(size_t)to * W4] = make_float4(fmaf(c, yv.x, a.x), fmaf(c, yv.y, a.y), fmaf(c, yv.z, a.z), fmaf(c, yv.w, a.w));
+            }
+        }
+    }
+}
+
 extern "C" int ce_streams_write(float* x, const float* y, const float* mix, const float* c_out, const float* bias,
                                 int T, int S, int W, cudaStream_t stream) {
     if (T == 0) return CE_OK;
@@ -257,6 +298,13 @@ extern "C" int ce_streams_write(float* x, const float* y, const float* mix, cons
     if (S <= 0 || S > ST_MAX_STREAMS) return ce_fail(CE_ERR_SIZE, "ce_streams_write: %d streams (1..%d)", S, ST_MAX_STREAMS);
     size_t total = (size_t)T * W;
     int blocks = (int)((total + 255) / 256 < (size_t)148 * 16 ? (total + 255) / 256 : (size_t)148 * 16);
+    if (W % 4 == 0 && S <= 4 && ((((uintptr_t)x | (uintptr_t)y | (uintptr_t)bias)) & 15) == 0) {
+        size_t total4 = total / 4;
+        int vblocks = (int)((total4 + 255) / 256 < (size_t)148 * 16 ? (total4 + 255) / 256 : (size_t)148 * 16);
+        ce_note("streams_write_vec_kernel");
+        ce_launch(streams_write_vec_kernel<4>, vblocks, 256, 0, stream, x, y, mix, c_out, bias, S, W / 4, total4);
+        return ce_check_launch("ce_streams_write");
+    }
     ce_note("streams_write_kernel");
     if (S <= 4) ce_launch(streams_write_kernel<4>, blocks, 256, 0, stream, x, y, mix, c_out, bias, S, W, total);
     else if (S <= 8) ce_launch(streams_write_kernel<8>, blocks, 256, 0, stream, x, y, mix, c_out, bias, S, W, total);

@@ -329,3 +329,29 @@ def test_trace_replay_program_on_a_munizen_folder(tmp_path):
     got2 = np.fromfile(os.path.join(out, "2.f32"), dtype="<f4").reshape(2, -1)
     assert not os.path.exists(os.path.join(out, "1.f32"))
     assert rel_err(got0, want[[0, 24]]) < 2e-4 and rel_err(got2, want[[39, 2]]) < 2e-4
+
+
+def test_command_line_writes_and_generates_a_munizen_model(tmp_path):
+    """``tiny-model --arch munizen`` then ``generate``: the printed ids are the plain implementation's greedy ones."""
+    import ast, os, re, subprocess, sys
+    from helpers import ROOT
+    carbon = [sys.executable, os.path.join(ROOT, "bin", "carbon")]
+    out = str(tmp_path / "tiny_m")
+    p = subprocess.run(carbon + ["tiny-model", "--arch", "munizen", "--out", out, "--layers", "4", "--hidden", "48", "--heads", "3",
+                                 "--kv-heads", "1", "--head-dim", "16", "--vocab", "120", "--seed", "9", "--streams", "3",
+                                 "--mask-size", "6", "--max-positions", "256"], capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0 and "wrote" in p.stdout, p.stderr[-2000:]
+    cfg, w = plain.read_model(out)
+    assert cfg["architecture"] == "Munizen" and cfg["streams"] == 3 and len(cfg["layers"]) == 4
+    prompt = tokens_of(np.random.default_rng(5), 17, 120)
+    p = subprocess.run(carbon + ["generate", "--model", out, "--prompt-ids", ",".join(map(str, prompt)), "--max-tokens", "8",
+                                 "--ignore-eos", "--print-ids", "--dtype", "f32", "--kv-tokens", "256", "--page-size", "16"],
+                       capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    ids = [ast.literal_eval(m) for m in re.findall(r"output_ids: (\[[^\]]*\])", p.stderr)][0]
+    toks = list(prompt)
+    for t in ids:
+        row = plain.forward(cfg, w, toks)[-1]
+        assert t == int(row.argmax()) or float(row.max() - row[t]) < 4e-4 * float(row.abs().max())
+        toks.append(t)
+    assert len(ids) == 8
