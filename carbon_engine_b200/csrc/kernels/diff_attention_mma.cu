@@ -17,6 +17,7 @@
 
 #define FA_BM 64
 #define FA_BN 64
+#define FA_SUB 32                // keys of a tile whose scores a warp holds at a time
 #define FA_THREADS 256
 #define FA_PAD 8                 // bf16 elements of padding per shared-memory row (16 bytes: conflict-free ldmatrix)
 
@@ -55,7 +56,7 @@ __device__ __forceinline__ unsigned fa_pack(float lo, float hi) {
 
 // DK: 16-element steps of a map the registers hold (d <= 16 DK); DVT: 8-column tiles of a value head (dv <= 8 DVT)
 template <int DK, int DVT>
-__global__ void __launch_bounds__(FA_THREADS) diff_attention_mma_kernel(FlashDiffArgs a) {
+__global__ void __launch_bounds__(FA_THREADS, (DVT <= 16 ? 2 : 1)) diff_attention_mma_kernel(FlashDiffArgs a) {
     ce_pdl_begin();
     extern __shared__ __align__(16) unsigned char fa_smem[];
     const int d = a.d, dv = a.dv, ldk = d + FA_PAD, ldv = dv + FA_PAD;
@@ -181,79 +182,88 @@ __global__ void __launch_bounds__(FA_THREADS) diff_attention_mma_kernel(FlashDif
         const __nv_bfloat16* Ks = stage0 + cur * stage_elems;
         const __nv_bfloat16* Vs = Ks + 2 * FA_BN * ldk;
 
-        float s[FA_BN / 8][4];
-#pragma unroll
-        for (int i = 0; i < FA_BN / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
         const __nv_bfloat16* Km = Ks + map * FA_BN * ldk;
+        // the tile's keys in two runs of FA_SUB: scores, softmax and P V of a run before the next (half the registers)
+#pragma unroll 1
+        for (int sub = 0; sub < FA_BN; sub += FA_SUB) {
+            const int ks0 = k0 + sub;
+            if (ks0 > pos_last) break;
+            float s[FA_SUB / 8][4];
 #pragma unroll
-        for (int ks = 0; ks < DK; ++ks) {
-            if (ks * 16 < d) {
+            for (int i = 0; i < FA_SUB / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
 #pragma unroll
-                for (int nt = 0; nt < FA_BN / 8; nt += 2) {
-                    unsigned b0, b1, b2, b3;
-                    fa_ldmatrix_x4(b0, b1, b2, b3, Km + (nt * 8 + (lane >> 4) * 8 + (lane & 7)) * ldk + ks * 16 + ((lane >> 3) & 1) * 8);
-                    fa_mma(s[nt], qf[ks], b0, b1);
-                    fa_mma(s[nt + 1], qf[ks], b2, b3);
+            for (int ks = 0; ks < DK; ++ks) {
+                if (ks * 16 < d) {
+#pragma unroll
+                    for (int nt = 0; nt < FA_SUB / 8; nt += 2) {
+                        unsigned b0, b1, b2, b3;
+                        fa_ldmatrix_x4(b0, b1, b2, b3, Km + (sub + nt * 8 + (lane >> 4) * 8 + (lane & 7)) * ldk + ks * 16 + ((lane >> 3) & 1) * 8);
+                        fa_mma(s[nt], qf[ks], b0, b1);
+                        fa_mma(s[nt + 1], qf[ks], b2, b3);
+                    }
                 }
             }
-        }
-        // scale, mask, running maximum
-        float mx_a = -INFINITY, mx_b = -INFINITY;
-        if (rows_full && k0 + FA_BN - 1 <= warp_pos_first && k0 >= warp_lo_last) {
+            // scale, mask, running maximum
+            float mx_a = -INFINITY, mx_b = -INFINITY;
+            if (rows_full && ks0 + FA_SUB - 1 <= warp_pos_first && ks0 >= warp_lo_last) {
 #pragma unroll
-            for (int nt = 0; nt < FA_BN / 8; ++nt) {
-                s[nt][0] *= a.scale; s[nt][1] *= a.scale; s[nt][2] *= a.scale; s[nt][3] *= a.scale;
-                mx_a = fmaxf(mx_a, fmaxf(s[nt][0], s[nt][1]));
-                mx_b = fmaxf(mx_b, fmaxf(s[nt][2], s[nt][3]));
-            }
-        } else {
+                for (int nt = 0; nt < FA_SUB / 8; ++nt) {
+                    s[nt][0] *= a.scale; s[nt][1] *= a.scale; s[nt][2] *= a.scale; s[nt][3] *= a.scale;
+                    mx_a = fmaxf(mx_a, fmaxf(s[nt][0], s[nt][1]));
+                    mx_b = fmaxf(mx_b, fmaxf(s[nt][2], s[nt][3]));
+                }
+            } else {
 #pragma unroll
-            for (int nt = 0; nt < FA_BN / 8; ++nt) {
+                for (int nt = 0; nt < FA_SUB / 8; ++nt) {
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    int key = k0 + nt * 8 + (lane & 3) * 2 + (e & 1);
-                    bool upper = e < 2;
-                    bool see = upper ? (key <= pos_a && key >= lo_a) : (key <= pos_b && key >= lo_b);
-                    float v = see ? s[nt][e] * a.scale : -INFINITY;
-                    s[nt][e] = v;
-                    if (upper) mx_a = fmaxf(mx_a, v); else mx_b = fmaxf(mx_b, v);
+                    for (int e = 0; e < 4; ++e) {
+                        int key = ks0 + nt * 8 + (lane & 3) * 2 + (e & 1);
+                        bool upper = e < 2;
+                        bool see = upper ? (key <= pos_a && key >= lo_a) : (key <= pos_b && key >= lo_b);
+                        float v = see ? s[nt][e] * a.scale : -INFINITY;
+                        s[nt][e] = v;
+                        if (upper) mx_a = fmaxf(mx_a, v); else mx_b = fmaxf(mx_b, v);
+                    }
                 }
             }
-        }
-        mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1)); mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
-        mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1)); mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
-        float n_a = fmaxf(m_a, mx_a), n_b = fmaxf(m_b, mx_b);
-        float use_a = n_a == -INFINITY ? 0.f : n_a, use_b = n_b == -INFINITY ? 0.f : n_b;
-        float f_a = m_a == -INFINITY ? 0.f : ce_exp2_fast((m_a - use_a) * LOG2E);
-        float f_b = m_b == -INFINITY ? 0.f : ce_exp2_fast((m_b - use_b) * LOG2E);
-        m_a = n_a; m_b = n_b;
-        float sum_a = 0.f, sum_b = 0.f;
-        unsigned pf[FA_BN / 16][4];
+            mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1)); mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
+            mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1)); mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
+            float n_a = fmaxf(m_a, mx_a), n_b = fmaxf(m_b, mx_b);
+            float use_a = n_a == -INFINITY ? 0.f : n_a, use_b = n_b == -INFINITY ? 0.f : n_b;
+            float f_a = m_a == -INFINITY ? 0.f : ce_exp2_fast((m_a - use_a) * LOG2E);
+            float f_b = m_b == -INFINITY ? 0.f : ce_exp2_fast((m_b - use_b) * LOG2E);
+            const bool moved = n_a != m_a || n_b != m_b;
+            m_a = n_a; m_b = n_b;
+            float sum_a = 0.f, sum_b = 0.f;
+            unsigned pf[FA_SUB / 16][4];
 #pragma unroll
-        for (int nt = 0; nt < FA_BN / 8; ++nt) {
-            float p0 = ce_exp2_fast((s[nt][0] - use_a) * LOG2E), p1 = ce_exp2_fast((s[nt][1] - use_a) * LOG2E);
-            float p2 = ce_exp2_fast((s[nt][2] - use_b) * LOG2E), p3 = ce_exp2_fast((s[nt][3] - use_b) * LOG2E);
-            sum_a += p0 + p1;
-            sum_b += p2 + p3;
-            pf[nt >> 1][(nt & 1) * 2] = fa_pack(p0, p1);
-            pf[nt >> 1][(nt & 1) * 2 + 1] = fa_pack(p2, p3);
-        }
-        sum_a += __shfl_xor_sync(0xffffffffu, sum_a, 1); sum_a += __shfl_xor_sync(0xffffffffu, sum_a, 2);
-        sum_b += __shfl_xor_sync(0xffffffffu, sum_b, 1); sum_b += __shfl_xor_sync(0xffffffffu, sum_b, 2);
-        l_a = l_a * f_a + sum_a;
-        l_b = l_b * f_b + sum_b;
+            for (int nt = 0; nt < FA_SUB / 8; ++nt) {
+                float p0 = ce_exp2_fast((s[nt][0] - use_a) * LOG2E), p1 = ce_exp2_fast((s[nt][1] - use_a) * LOG2E);
+                float p2 = ce_exp2_fast((s[nt][2] - use_b) * LOG2E), p3 = ce_exp2_fast((s[nt][3] - use_b) * LOG2E);
+                sum_a += p0 + p1;
+                sum_b += p2 + p3;
+                pf[nt >> 1][(nt & 1) * 2] = fa_pack(p0, p1);
+                pf[nt >> 1][(nt & 1) * 2 + 1] = fa_pack(p2, p3);
+            }
+            sum_a += __shfl_xor_sync(0xffffffffu, sum_a, 1); sum_a += __shfl_xor_sync(0xffffffffu, sum_a, 2);
+            sum_b += __shfl_xor_sync(0xffffffffu, sum_b, 1); sum_b += __shfl_xor_sync(0xffffffffu, sum_b, 2);
+            l_a = l_a * f_a + sum_a;
+            l_b = l_b * f_b + sum_b;
+            if (__any_sync(0xffffffffu, moved)) {            // a maximum rose somewhere in the warp: what is summed so far shrinks
 #pragma unroll
-        for (int i = 0; i < DVT; ++i) { o[i][0] *= f_a; o[i][1] *= f_a; o[i][2] *= f_b; o[i][3] *= f_b; }
-        // O += P V
+                for (int i = 0; i < DVT; ++i) { o[i][0] *= f_a; o[i][1] *= f_a; o[i][2] *= f_b; o[i][3] *= f_b; }
+            }
+            // O += P V
 #pragma unroll
-        for (int kk = 0; kk < FA_BN / 16; ++kk) {
+            for (int kk = 0; kk < FA_SUB / 16; ++kk) {
 #pragma unroll
-            for (int nt = 0; nt < DVT; nt += 2) {
-                if (nt * 8 < dv) {
-                    unsigned b0, b1, b2, b3;
-                    fa_ldmatrix_x4_trans(b0, b1, b2, b3, Vs + (kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * ldv + nt * 8 + (lane >> 4) * 8);
-                    fa_mma(o[nt], pf[kk], b0, b1);
-                    fa_mma(o[nt + 1], pf[kk], b2, b3);
+                for (int nt = 0; nt < DVT; nt += 2) {
+                    if (nt * 8 < dv) {
+                        unsigned b0, b1, b2, b3;
+                        fa_ldmatrix_x4_trans(b0, b1, b2, b3, Vs + (sub + kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * ldv + nt * 8 + (lane >> 4) * 8);
+                        fa_mma(o[nt], pf[kk], b0, b1);
+                        fa_mma(o[nt + 1], pf[kk], b2, b3);
+                    }
                 }
             }
         }
