@@ -69,7 +69,9 @@ __global__ void __launch_bounds__(FA_THREADS, (DVT <= 16 ? 2 : 1)) diff_attentio
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int map = warp >> 2, row0 = (warp & 3) * 16;
-    const int b = a.tiles[2 * blockIdx.x], q0 = a.tiles[2 * blockIdx.x + 1], h = blockIdx.y;
+    // the tile list is in the order of the tokens; the later tiles of a sequence see the most keys, and go first
+    const int tile = gridDim.x - 1 - blockIdx.x;
+    const int b = a.tiles[2 * tile], q0 = a.tiles[2 * tile + 1], h = blockIdx.y;
     const int kvh = h / (a.nh / a.nkv);
     const int t0 = a.q_start[b] + q0, n_rows = min(FA_BM, a.q_start[b + 1] - t0);
     const int* table = a.block_table + (size_t)a.seq_slot[b] * a.max_pages;
@@ -104,7 +106,8 @@ __global__ void __launch_bounds__(FA_THREADS, (DVT <= 16 ? 2 : 1)) diff_attentio
 #pragma unroll
     for (int i = 0; i < DVT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
-    const float LOG2E = 1.4426950408889634f;
+    // scores are kept in the base-2 domain: one multiplication by scale * log2(e), then 2^(s - m) is one subtraction and one MUFU
+    const float scale2 = a.scale * 1.4426950408889634f;
 
     // the page of key row r of the tile at k0, or -1 (no such key, or a page the request does not hold)
     auto page_of = [&](int k0, int r) -> int {
@@ -208,7 +211,7 @@ __global__ void __launch_bounds__(FA_THREADS, (DVT <= 16 ? 2 : 1)) diff_attentio
             if (rows_full && ks0 + FA_SUB - 1 <= warp_pos_first && ks0 >= warp_lo_last) {
 #pragma unroll
                 for (int nt = 0; nt < FA_SUB / 8; ++nt) {
-                    s[nt][0] *= a.scale; s[nt][1] *= a.scale; s[nt][2] *= a.scale; s[nt][3] *= a.scale;
+                    s[nt][0] *= scale2; s[nt][1] *= scale2; s[nt][2] *= scale2; s[nt][3] *= scale2;
                     mx_a = fmaxf(mx_a, fmaxf(s[nt][0], s[nt][1]));
                     mx_b = fmaxf(mx_b, fmaxf(s[nt][2], s[nt][3]));
                 }
@@ -220,7 +223,7 @@ __global__ void __launch_bounds__(FA_THREADS, (DVT <= 16 ? 2 : 1)) diff_attentio
                         int key = ks0 + nt * 8 + (lane & 3) * 2 + (e & 1);
                         bool upper = e < 2;
                         bool see = upper ? (key <= pos_a && key >= lo_a) : (key <= pos_b && key >= lo_b);
-                        float v = see ? s[nt][e] * a.scale : -INFINITY;
+                        float v = see ? s[nt][e] * scale2 : -INFINITY;
                         s[nt][e] = v;
                         if (upper) mx_a = fmaxf(mx_a, v); else mx_b = fmaxf(mx_b, v);
                     }
@@ -230,16 +233,16 @@ __global__ void __launch_bounds__(FA_THREADS, (DVT <= 16 ? 2 : 1)) diff_attentio
             mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1)); mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
             float n_a = fmaxf(m_a, mx_a), n_b = fmaxf(m_b, mx_b);
             float use_a = n_a == -INFINITY ? 0.f : n_a, use_b = n_b == -INFINITY ? 0.f : n_b;
-            float f_a = m_a == -INFINITY ? 0.f : ce_exp2_fast((m_a - use_a) * LOG2E);
-            float f_b = m_b == -INFINITY ? 0.f : ce_exp2_fast((m_b - use_b) * LOG2E);
+            float f_a = m_a == -INFINITY ? 0.f : ce_exp2_fast(m_a - use_a);
+            float f_b = m_b == -INFINITY ? 0.f : ce_exp2_fast(m_b - use_b);
             const bool moved = n_a != m_a || n_b != m_b;
             m_a = n_a; m_b = n_b;
             float sum_a = 0.f, sum_b = 0.f;
             unsigned pf[FA_SUB / 16][4];
 #pragma unroll
             for (int nt = 0; nt < FA_SUB / 8; ++nt) {
-                float p0 = ce_exp2_fast((s[nt][0] - use_a) * LOG2E), p1 = ce_exp2_fast((s[nt][1] - use_a) * LOG2E);
-                float p2 = ce_exp2_fast((s[nt][2] - use_b) * LOG2E), p3 = ce_exp2_fast((s[nt][3] - use_b) * LOG2E);
+                float p0 = ce_exp2_fast(s[nt][0] - use_a), p1 = ce_exp2_fast(s[nt][1] - use_a);
+                float p2 = ce_exp2_fast(s[nt][2] - use_b), p3 = ce_exp2_fast(s[nt][3] - use_b);
                 sum_a += p0 + p1;
                 sum_b += p2 + p3;
                 pf[nt >> 1][(nt & 1) * 2] = fa_pack(p0, p1);

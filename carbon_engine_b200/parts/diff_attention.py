@@ -103,8 +103,15 @@ class DifferentialAttention(Mixer):
             el, keys, pairs = qkvg.element_size(), 0, 0
             for b in range(ctx.B):
                 n, before = ctx.h_q_start[b + 1] - ctx.h_q_start[b], ctx.h_ctx_before[b]
-                keys += before + n
-                pairs += n * before + n * (n + 1) // 2      # an upper bound: chunks and windows see fewer
+                first = before
+                if self.chunk > 0:
+                    first = max(first - first % self.chunk, 0)
+                keys += before + n - (first if self.chunk > 0 else 0)
+                for p in range(before, before + n):          # the keys position p sees
+                    lo = max(0, p - self.window + 1) if self.window > 0 else 0
+                    if self.chunk > 0:
+                        lo = max(lo, p - p % self.chunk)
+                    pairs += p - lo + 1
             prof.note_work((keys * G * (2 * d + dv) + ctx.T * H * (2 * d + dv)) * el, 4 * pairs * H * (d + dv))
         consts = (self.window, self.chunk, self.scale, self.lam, self.eps, 1.0 - self.diff)
         stride = qkvg.stride(0)
