@@ -22,7 +22,6 @@ from typing import List, Optional
 import torch
 
 from .. import ops
-from .attention import PagedAttention
 from .base import Mixer, PagedCacheSpec, Part, TensorGetter, TensorSpec, register_init_kind
 from .linear import ACCUM, STORE, STORE_F32, Linear
 from .rope import PositionEncoding
@@ -30,14 +29,17 @@ from .rope import PositionEncoding
 register_init_kind("lambda_vec", 0.0, 0.1, True)
 
 
+class DiffAttentionPlan:
+    def __init__(self, tiles, n_tiles):
+        self.tiles, self.n_tiles = tiles, n_tiles
+        self.graph_key = None            # a decode step of B sequences is always B tiles
+
+
 class DifferentialAttention(Mixer):
     graph_safe = True
     can_store = True
-    # the step's tiles of query tokens are those of the paged attention: one plan serves every attention layer
-    plan_key = PagedAttention.plan_key
-    TILE, TILE_TC = PagedAttention.TILE, PagedAttention.TILE_TC
-    step_sections = PagedAttention.step_sections
-    plan_step = PagedAttention.plan_step
+    plan_key = "differential_attention"
+    TILE = 64               # query tokens a block of the tensor-core kernel takes
 
     def __init__(self, hidden: int, heads: int, kv_heads: int, dim: int, vdim: int, prefix: str, diff: float, eps: float,
                  position: Optional[PositionEncoding] = None, scale: Optional[float] = None, chunk: int = 0,
@@ -74,6 +76,21 @@ class DifferentialAttention(Mixer):
 
     def step_bytes(self, tokens: int, element_size: int) -> int:
         return tokens * (self.qkvg.padded_out + self.heads * self.vdim) * element_size
+
+    def step_sections(self, max_tokens: int, max_seqs: int):
+        return [("differential_attention.tiles", 2 * (max_seqs + max_tokens // self.TILE + 1))]
+
+    def plan_step(self, ctx) -> "DiffAttentionPlan":
+        """The step's tiles of up to 64 query tokens, (sequence, first token) pairs, of EVERY sequence: one-token
+        sequences are tiles of one row (a query sees at most a mask block of keys, so there is nothing to split
+        among blocks, and a block per sequence and head on the tensor-core kernel is the shortest way)."""
+        tiles = ctx.bufs.host_section("differential_attention.tiles")
+        n = 0
+        for b in range(ctx.B):
+            for q0 in range(0, ctx.h_q_start[b + 1] - ctx.h_q_start[b], self.TILE):
+                tiles[2 * n], tiles[2 * n + 1] = b, q0
+                n += 1
+        return DiffAttentionPlan(ctx.bufs.dev_section("differential_attention.tiles"), n)
 
     def forward(self, ctx, h: torch.Tensor, x: torch.Tensor, cache, accumulate: bool = True) -> None:
         T = h.shape[0]
@@ -115,16 +132,11 @@ class DifferentialAttention(Mixer):
             prof.note_work((keys * G * (2 * d + dv) + ctx.T * H * (2 * d + dv)) * el, 4 * pairs * H * (d + dv))
         consts = (self.window, self.chunk, self.scale, self.lam, self.eps, 1.0 - self.diff)
         stride = qkvg.stride(0)
-        n_plain = ctx.T
         if qkvg.dtype == torch.bfloat16 and ctx.fast_attention and ops.diff_attention_mma_supported(d, dv, stride):
-            # portions of prompts on the tensor cores, a tile of 64 query tokens a block; the one-token sequences
-            # (they come first in a step) on the float32 kernel, whose block is one (token, head)
             plan = ctx.plans[self.plan_key]
-            if plan.n_tiles > 0:
-                ops.diff_attention_mma(qkvg, stride, cache.k_pool, cache.v_pool, gate, stride, out, ctx.positions, ctx.seq_slot,
-                                       ctx.q_start, table, plan.tiles, plan.n_tiles, ctx.status, H, G, d, dv, cache.page_size,
-                                       *consts)
-            n_plain = ctx.n_decode
-        if n_plain > 0:
-            ops.diff_attention(qkvg, stride, cache.k_pool, cache.v_pool, gate, stride, out, ctx.positions, ctx.seq_of_token,
-                               ctx.seq_slot, table, ctx.status, H, G, d, dv, cache.page_size, *consts, n_tokens=n_plain)
+            ops.diff_attention_mma(qkvg, stride, cache.k_pool, cache.v_pool, gate, stride, out, ctx.positions, ctx.seq_slot,
+                                   ctx.q_start, table, plan.tiles, plan.n_tiles, ctx.status, H, G, d, dv, cache.page_size,
+                                   *consts)
+            return
+        ops.diff_attention(qkvg, stride, cache.k_pool, cache.v_pool, gate, stride, out, ctx.positions, ctx.seq_of_token,
+                           ctx.seq_slot, table, ctx.status, H, G, d, dv, cache.page_size, *consts)
