@@ -57,6 +57,17 @@ CASES: Dict[str, dict] = {
     "S": config([delta_layer(heads=2, dim=32, rank=6), attention_layer(heads=6, kv_heads=2, dim=12, vdim=20, rot=(4, 77.0), mask=5),
                  delta_layer(heads=5, dim=12, rank=9)], width=60, vocab=211, groups=4, streams=4, loop=(1, 2, 3)),
 }
+# Head sizes the tensor-core attention kernel takes (multiples of 16): small maps with larger values and groups of two
+# heads; and maps over 64 with values over 128 (the kernel's larger register layouts), one key head for all.
+CASES["T"] = config([attention_layer(heads=4, kv_heads=2, dim=32, vdim=64, rot=(16, 10000.0), mask=37, scale=0.18, ff=72),
+                     delta_layer(heads=2, dim=32, rank=8)], width=64, vocab=151, groups=2, streams=2, loop=(0, 2, 2))
+CASES["U"] = config([delta_layer(heads=1, dim=48, rank=8), attention_layer(heads=2, kv_heads=1, dim=80, vdim=144, rot=(80, 3000.0),
+                                                                           mask=100, scale=0.11, diff=0.45, ff=None)],
+                    width=96, vocab=89, groups=3, streams=3)
+# The head sizes of a mid-sized model: maps of 64, values of 128, state heads of 64.
+CASES["V"] = config([delta_layer(heads=4, dim=64, rank=16), attention_layer(heads=4, kv_heads=2, dim=64, vdim=128, rot=(32, 1e6),
+                                                                            mask=50, scale=0.125, ff=384)],
+                    width=256, vocab=300, groups=2, streams=2)
 #: one layer of one kind each, for looking at a mechanism alone
 SINGLE = {
     "attention": config([attention_layer(ff=None)], streams=None, groups=1),

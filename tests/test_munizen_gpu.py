@@ -123,12 +123,16 @@ def test_layers_outputs_one_after_another(tmp_path):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", sorted(CASES))
 def test_whole_prompt_portions_and_decoding(tmp_path, name, dtype):
+    from carbon_engine_b200 import ops
     folder = write_model(CASES[name], str(tmp_path / name), seed=11)
     rng = np.random.default_rng(3)
     toks = tokens_of(rng, 83, CASES[name]["vocab"])
     want = plain_logits(folder, toks)
     h = Harness(folder, dtype, page_size=8, pages=16)          # 128 tokens of pages: every run reuses the last one's
+    ops.reset_kernel_counts()
     whole = h.run(toks)
+    if name in ("T", "U", "V"):           # head sizes of the tensor-core kernel: bfloat16 must have taken it, float32 never
+        assert ("diff_attention_mma_kernel" in ops.kernel_counts()) == (dtype == "bfloat16")
     assert rel_err(whole, want) < TOL[dtype], "whole"
     for cuts in ([1], [2], [3, 2, 7, 2, 16, 5], [40, 1, 1, 1], [64, 19]):
         got = h.run(toks, cuts)
