@@ -12,9 +12,13 @@
 // every key row of a tile is looked up two tiles ahead, so that no copy waits for a table entry.
 //
 // One-token sequences of a decode step are tiles of one row: a query sees at most a mask block of keys, so there is
-// nothing to split among blocks.  Measured there and dropped, each without effect on the step (0.55 ms at batch 8 with
-// mask blocks of 1,024 nearly full): four buffers of tiles in flight instead of two, and the four warps of a map
-// sharing the key tiles with a merge at the end.
+// nothing to split among blocks.  Such a tile is work for one warp a map, and that warp's instructions, one after
+// another, are what the block's time is made of (about 1,700 a tile of 64 keys, 4.5 us).  So where the launch has no
+// more blocks than the GPU has SMs, the kernel gets four K/V buffers and the four warps of a map take four tiles of
+// keys side by side, each with a running maximum and sum of its own; their partial rows are merged through shared
+// memory in the order of the warps (batch 8, 16 heads, mask blocks of 1,024 nearly full: 0.56 -> 0.50 ms a step).
+// Measured and dropped: four buffers in flight with one warp still walking all tiles (no effect), and the warps taking
+// every fourth tile with the block still meeting at a barrier after each tile (no effect: the tiles stayed in a row).
 //
 // Visible keys per row: causal, optionally the last ``window``, optionally only the row's own block of
 // ``chunk`` positions; a tile of queries may straddle blocks, so the mask is applied per element.
@@ -39,6 +43,7 @@ struct FlashDiffArgs {
     const int* tiles;            // (sequence, first token of the tile within the sequence's tokens of the step)
     int* status;
     int nh, nkv, d, dv, q_stride, gate_stride, page_size, max_pages, num_pages, window, chunk;
+    int share;                   // 1: four K/V buffers are there, and tiles of at most 16 rows spread their key tiles over a map's warps
     float scale, lambda, eps, out_scale;
 };
 
@@ -70,15 +75,24 @@ __global__ void __launch_bounds__(FA_THREADS, (DVT <= 16 ? 2 : 1)) diff_attentio
     const int stage_elems = 2 * FA_BN * ldk + FA_BN * ldv;
     float* comb = (float*)stage0;                            // [64][dv] map 2's rows, once the key tiles are done
     __shared__ int s_pos[FA_BM];
-    __shared__ int s_page[2][FA_BN];                         // page of every key row of the tile a buffer will hold
+    __shared__ int s_page[4][FA_BN];                         // page of every key row of the tile a buffer will hold
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int map = warp >> 2, row0 = (warp & 3) * 16;
+    const int map = warp >> 2, part_of_map = warp & 3;
     // the tile list is in the order of the tokens; the later tiles of a sequence see the most keys, and go first
     const int tile = gridDim.x - 1 - blockIdx.x;
     const int b = a.tiles[2 * tile], q0 = a.tiles[2 * tile + 1], h = blockIdx.y;
     const int kvh = h / (a.nh / a.nkv);
     const int t0 = a.q_start[b] + q0, n_rows = min(FA_BM, a.q_start[b + 1] - t0);
+    // few rows: the warps of a map all take rows 0..15 and share the key tiles; else warp w of a map takes rows 16 w ..
+    bool share_keys = a.share != 0 && n_rows <= 16;
+    if (share_keys) {                // ... and only where there are at least two tiles of keys to share
+        int pf = a.positions[t0], pl = a.positions[t0 + n_rows - 1];
+        int lo = a.window > 0 ? max(0, pf - a.window + 1) : 0;
+        if (a.chunk > 0) lo = max(lo, pf / a.chunk * a.chunk);
+        share_keys = pl - lo / FA_BN * FA_BN >= FA_BN;
+    }
+    const int row0 = share_keys ? 0 : part_of_map * 16;
     const int* table = a.block_table + (size_t)a.seq_slot[b] * a.max_pages;
 
     if (tid < FA_BM) s_pos[tid] = tid < n_rows ? a.positions[t0 + tid] : -1;
@@ -167,26 +181,8 @@ __global__ void __launch_bounds__(FA_THREADS, (DVT <= 16 ? 2 : 1)) diff_attentio
         warp_lo_last = a.window > 0 ? max(0, pl - a.window + 1) : 0;
         if (a.chunk > 0) warp_lo_last = max(warp_lo_last, pl / a.chunk * a.chunk);
     }
-    const int k_first = lo_blk / FA_BN * FA_BN;
-    if (tid < FA_BN) {
-        s_page[0][tid] = page_of(k_first, tid);
-        s_page[1][tid] = page_of(k_first + FA_BN, tid);
-    }
-    __syncthreads();
-    stage(k_first, 0);
-    int it = 0;
-    for (int k0 = k_first; k0 <= pos_last; k0 += FA_BN, ++it) {
-        const int cur = it & 1;
-        const bool more = k0 + FA_BN <= pos_last;
-        int page_ahead = -1;                        // for the tile after the next: asked for now, stored after the arithmetic
-        if (tid < FA_BN && more) page_ahead = page_of(k0 + 2 * FA_BN, tid);
-        if (more) {
-            stage(k0 + FA_BN, cur ^ 1);
-            asm volatile("cp.async.wait_group 1;" ::: "memory");
-        } else {
-            asm volatile("cp.async.wait_group 0;" ::: "memory");
-        }
-        __syncthreads();
+    // scores, softmax and P V of the tile of keys at k0, which lies in buffer ``cur``
+    auto tile_math = [&](int k0, int cur) {
         const __nv_bfloat16* Ks = stage0 + cur * stage_elems;
         const __nv_bfloat16* Vs = Ks + 2 * FA_BN * ldk;
 
@@ -278,12 +274,107 @@ __global__ void __launch_bounds__(FA_THREADS, (DVT <= 16 ? 2 : 1)) diff_attentio
             }
         }
         }
-        if (tid < FA_BN) s_page[cur][tid] = page_ahead;      // buffer ``cur`` will hold the tile after the next
+    };
+    const int k_first = lo_blk / FA_BN * FA_BN;
+    if (!share_keys) {
+        if (tid < FA_BN) {
+            s_page[0][tid] = page_of(k_first, tid);
+            s_page[1][tid] = page_of(k_first + FA_BN, tid);
+        }
         __syncthreads();
+        stage(k_first, 0);
+        int it = 0;
+        for (int k0 = k_first; k0 <= pos_last; k0 += FA_BN, ++it) {
+            const int cur = it & 1;
+            const bool more = k0 + FA_BN <= pos_last;
+            int page_ahead = -1;                    // for the tile after the next: asked for now, stored after the arithmetic
+            if (tid < FA_BN && more) page_ahead = page_of(k0 + 2 * FA_BN, tid);
+            if (more) {
+                stage(k0 + FA_BN, cur ^ 1);
+                asm volatile("cp.async.wait_group 1;" ::: "memory");
+            } else {
+                asm volatile("cp.async.wait_group 0;" ::: "memory");
+            }
+            __syncthreads();
+            tile_math(k0, cur);
+            if (tid < FA_BN) s_page[cur][tid] = page_ahead;      // buffer ``cur`` will hold the tile after the next
+            __syncthreads();
+        }
+    } else {
+        // Four tiles of keys at a time, one for each warp of a map: a tile of one query row is work for one warp, whose
+        // instructions one after another are what the block's time is made of, so the warps take the tiles side by side
+        // and their partial rows are merged afterwards.
+        for (int g0 = k_first; g0 <= pos_last; g0 += 4 * FA_BN) {
+            if (tid < FA_BN)
+                for (int w = 0; w < 4; ++w) s_page[w][tid] = page_of(g0 + w * FA_BN, tid);
+            __syncthreads();
+            for (int w = 0; w < 4; ++w)
+                if (g0 + w * FA_BN <= pos_last) stage(g0 + w * FA_BN, w);
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+            __syncthreads();
+            if (g0 + part_of_map * FA_BN <= pos_last) tile_math(g0 + part_of_map * FA_BN, part_of_map);
+            __syncthreads();
+        }
     }
-    float i_a = l_a > 0.f ? 1.0f / l_a : 0.f, i_b = l_b > 0.f ? 1.0f / l_b : 0.f;
     const int cq = (lane & 3) * 2;
-    if (map == 1) {
+    if (share_keys) {
+        // partial rows of the four warps of each map, after the place of map 2's finished rows: the sums so far [2][4][16][dv]
+        // and (maximum, sum) [2][4][16][2]; warp 0 of each map then adds them up in the order of the warps
+        float* part = comb + FA_BM * dv;
+        float* ml = part + 2 * 4 * 16 * dv;
+        const int r_lo = lane >> 2, r_hi = r_lo + 8;
+        if (part_of_map != 0) {
+            float* mine = part + ((map * 4 + part_of_map) * 16) * dv;
+#pragma unroll
+            for (int nt = 0; nt < DVT; ++nt) {
+                if (nt * 8 < dv) {
+                    *reinterpret_cast<float2*>(mine + r_lo * dv + nt * 8 + cq) = make_float2(o[nt][0], o[nt][1]);
+                    *reinterpret_cast<float2*>(mine + r_hi * dv + nt * 8 + cq) = make_float2(o[nt][2], o[nt][3]);
+                }
+            }
+            if ((lane & 3) == 0) {
+                float* m2 = ml + ((map * 4 + part_of_map) * 16) * 2;
+                m2[r_lo * 2] = m_a; m2[r_lo * 2 + 1] = l_a;
+                m2[r_hi * 2] = m_b; m2[r_hi * 2 + 1] = l_b;
+            }
+        }
+        __syncthreads();
+        if (part_of_map == 0) {
+            float big_a = m_a, big_b = m_b;
+#pragma unroll
+            for (int w = 1; w < 4; ++w) {
+                const float* m2 = ml + ((map * 4 + w) * 16) * 2;
+                big_a = fmaxf(big_a, m2[r_lo * 2]);
+                big_b = fmaxf(big_b, m2[r_hi * 2]);
+            }
+            float f_a = m_a == -INFINITY ? 0.f : ce_exp2_fast(m_a - big_a), f_b = m_b == -INFINITY ? 0.f : ce_exp2_fast(m_b - big_b);
+            l_a *= f_a; l_b *= f_b;
+#pragma unroll
+            for (int i = 0; i < DVT; ++i) { o[i][0] *= f_a; o[i][1] *= f_a; o[i][2] *= f_b; o[i][3] *= f_b; }
+#pragma unroll
+            for (int w = 1; w < 4; ++w) {
+                const float* m2 = ml + ((map * 4 + w) * 16) * 2;
+                const float* theirs = part + ((map * 4 + w) * 16) * dv;
+                float ma = m2[r_lo * 2], mb = m2[r_hi * 2];
+                float g_a = ma == -INFINITY ? 0.f : ce_exp2_fast(ma - big_a), g_b = mb == -INFINITY ? 0.f : ce_exp2_fast(mb - big_b);
+                l_a = fmaf(m2[r_lo * 2 + 1], g_a, l_a);
+                l_b = fmaf(m2[r_hi * 2 + 1], g_b, l_b);
+#pragma unroll
+                for (int nt = 0; nt < DVT; ++nt) {
+                    if (nt * 8 < dv) {
+                        float2 xa = *reinterpret_cast<const float2*>(theirs + r_lo * dv + nt * 8 + cq);
+                        float2 xb = *reinterpret_cast<const float2*>(theirs + r_hi * dv + nt * 8 + cq);
+                        o[nt][0] = fmaf(xa.x, g_a, o[nt][0]); o[nt][1] = fmaf(xa.y, g_a, o[nt][1]);
+                        o[nt][2] = fmaf(xb.x, g_b, o[nt][2]); o[nt][3] = fmaf(xb.y, g_b, o[nt][3]);
+                    }
+                }
+            }
+        }
+        __syncthreads();             // the partial rows are read before map 2's finished rows go to the same memory's start
+    }
+    const bool finishes = !share_keys || part_of_map == 0;       // the warps that hold finished rows
+    float i_a = l_a > 0.f ? 1.0f / l_a : 0.f, i_b = l_b > 0.f ? 1.0f / l_b : 0.f;
+    if (map == 1 && finishes) {
 #pragma unroll
         for (int nt = 0; nt < DVT; ++nt) {
             if (nt * 8 < dv) {
@@ -293,7 +384,7 @@ __global__ void __launch_bounds__(FA_THREADS, (DVT <= 16 ? 2 : 1)) diff_attentio
         }
     }
     __syncthreads();
-    if (map == 0) {
+    if (map == 0 && finishes) {
         float ss_a = 0.f, ss_b = 0.f;
 #pragma unroll
         for (int nt = 0; nt < DVT; ++nt) {
@@ -332,7 +423,7 @@ extern "C" int ce_diff_attention_mma_supported(int d, int dv, int q_stride) {
 
 template <int DK, int DVT>
 static void launch_flash_diff(const FlashDiffArgs& a, int n_tiles, cudaStream_t stream) {
-    size_t smem = (size_t)(2 * FA_BM * (a.d + FA_PAD) + 2 * (2 * FA_BN * (a.d + FA_PAD) + FA_BN * (a.dv + FA_PAD))) * sizeof(__nv_bfloat16);
+    size_t smem = (size_t)(2 * FA_BM * (a.d + FA_PAD) + (a.share ? 4 : 2) * (2 * FA_BN * (a.d + FA_PAD) + FA_BN * (a.dv + FA_PAD))) * sizeof(__nv_bfloat16);
     if (smem > 40 * 1024)            // the kernel's static arrays count toward the 48 KB a launch gets without asking
         cudaFuncSetAttribute(diff_attention_mma_kernel<DK, DVT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     ce_note("diff_attention_mma_kernel");
@@ -355,7 +446,15 @@ extern "C" int ce_diff_attention_mma(const void* q, const void* k_pool, const vo
         return ce_fail(CE_ERR_SIZE, "ce_diff_attention_mma: operands must be 16-byte aligned");
     FlashDiffArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, (const __nv_bfloat16*)gate,
                     (__nv_bfloat16*)out, positions, seq_slot, q_start, block_table, tiles, status, nh, nkv, d, dv, q_stride,
-                    gate_stride, page_size, max_pages, num_pages, window, chunk, scale, lambda, eps, out_scale};
+                    gate_stride, page_size, max_pages, num_pages, window, chunk, 0, scale, lambda, eps, out_scale};
+    // Few blocks (a decode step: a block per sequence and head): four buffers, so that the warps of a map can take four tiles
+    // of keys side by side, if they and the partial rows to merge fit; many blocks (prompts): two buffers, two blocks an SM.
+    if ((long long)n_tiles * nh <= (long long)ce_sm_count()) {       // one block an SM then: more blocks than SMs would wait their turn
+        size_t q_bytes = (size_t)2 * FA_BM * (d + FA_PAD) * sizeof(__nv_bfloat16);
+        size_t stage_bytes = (size_t)(2 * FA_BN * (d + FA_PAD) + FA_BN * (dv + FA_PAD)) * sizeof(__nv_bfloat16);
+        size_t merge_bytes = (size_t)(FA_BM * dv + 2 * 4 * 16 * dv + 2 * 4 * 16 * 2) * sizeof(float);
+        if (q_bytes + 4 * stage_bytes <= 200 * 1024 && merge_bytes <= 4 * stage_bytes) a.share = 1;
+    }
     if (d <= 64) {
         if (dv <= 64) launch_flash_diff<4, 8>(a, n_tiles, stream);
         else if (dv <= 128) launch_flash_diff<4, 16>(a, n_tiles, stream);
