@@ -21,8 +21,8 @@ _SIGNATURES = {
     "ce_kernel_counts_reset": (None, []),
     "ce_last_kernel": (ctypes.c_char_p, []),
     "ce_set_pdl": (None, [_i]),
-    # table, dtype, tokens, x, T, H, V, status, stream
-    "ce_embed": (_i, [_p, _i, _p, _p, _i, _i, _i, _p, _p]),
+    # table, dtype, tokens, x, T, H, V, status, scale, stream
+    "ce_embed": (_i, [_p, _i, _p, _p, _i, _i, _i, _p, _f, _p]),
     # x, w, out, out_dtype, rows, R, H, eps, stream
     "ce_rmsnorm": (_i, [_p, _p, _p, _i, _p, _i, _i, _f, _p]),
     # qkv, k_pool, v_pool, dtype, qw, kw, cos, sin, positions, seq_of_token, seq_slot, block_table, status,
@@ -31,6 +31,34 @@ _SIGNATURES = {
                                 _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _p]),
     "ce_add_residual": (_i, [_p, _p, _i, _ll, _p]),
     "ce_swiglu": (_i, [_p, _p, _i, _i, _i, _p]),
+    "ce_reluglu": (_i, [_p, _p, _i, _i, _i, _p]),
+    # x, w, b, out, out_dtype, rows, R, H, eps, stream
+    "ce_layernorm": (_i, [_p, _p, _p, _p, _i, _p, _i, _i, _f, _p]),
+    # y, w, x, T, H, eps, stream
+    "ce_rmsnorm_add": (_i, [_p, _p, _p, _i, _i, _f, _p]),
+    # x, n, cap, stream
+    "ce_tanh_cap": (_i, [_p, _ll, _f, _p]),
+    # src, out, out_dtype, T, ld, off, L, stream
+    "ce_copy_cols": (_i, [_p, _p, _i, _i, _i, _i, _i, _p]),
+    # z, table, dtype, tokens, out, T, D, ld, off, V, status, stream
+    "ce_side_gate": (_i, [_p, _p, _i, _p, _p, _i, _i, _i, _i, _i, _p, _p]),
+    # rows, dtype, stride, off, n, first, first_stride, first_off, lam, T, stream
+    "ce_value_mix": (_i, [_p, _i, _i, _i, _i, _p, _i, _i, _f, _i, _p]),
+    # proj, wq, wkv, cq, k_pool, dtype, cos, sin, positions, seq_of_token, seq_slot, block_table, status,
+    # T, ld, off_q, qr, off_kv, r, dr, rd, page_size, max_pages, num_pages, max_pos, write_kv, eps, stream
+    "ce_latent_prepare": (_i, [_p] * 5 + [_i] + [_p] * 7 + [_i] * 13 + [_f, _p]),
+    # src, src_stride, src_head, src_off, dst, dst_stride, dst_head, dst_off, dtype, cos, sin, positions, status,
+    # T, H, dr, rd, max_pos, stream
+    "ce_rope_part": (_i, [_p, _i, _i, _i, _p, _i, _i, _i, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p]),
+    # in, in_stride, in_head, W, out, out_stride, out_head, gate, gate_stride, dtype, M, H, N, K, stream
+    "ce_head_matmul": (_i, [_p, _i, _i, _p, _p, _i, _i, _p, _i, _i, _i, _i, _i, _i, _p]),
+    # q, k_pool, v_pool, gate, out, dtype, positions, seq_of_token, seq_slot, block_table, status, T, nh, nkv, d, dv,
+    # q_stride, q_head, ldk, ldv, gate_stride, page_size, max_pages, num_pages, window, keep_first, scale, softcap, stream
+    "ce_masked_attention": (_i, [_p] * 5 + [_i] + [_p] * 5 + [_i] * 15 + [_f, _f, _p]),
+    "ce_gated_delta_prep_width": (_i, [_i, _i, _i, _i]),
+    # proj, dec, gz, taps, a_log, dt_bias, norm_w, prep, raw, state, kept, out, out_dtype, seq_of_token, seq_slot, q_start,
+    # T, B, ld, off_conv, off_b, H, G, d, dv, K, eps, stage, stream
+    "ce_gated_delta": (_i, [_p] * 12 + [_i] + [_p] * 3 + [_i] * 10 + [_f, _i, _p]),
     # q, k_pool, v_pool, out, dtype, positions, seq_of_token, seq_slot, block_table, status,
     # T, nh, nkv, d, q_stride, page_size, max_pages, num_pages, window, scale, stream
     "ce_attention_generic": (_i, [_p, _p, _p, _p, _i, _p, _p, _p, _p, _p,

@@ -8,11 +8,11 @@
 #include "common.cuh"
 
 // ---------------------------------------------------------------------------------------------
-// Embedding: x[t, :] = float(table[token[t], :])
+// Embedding: x[t, :] = float(table[token[t], :]) * scale
 // ---------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ tokens,
-                             float* __restrict__ x, int H, int V, int* __restrict__ status) {
+                             float* __restrict__ x, int H, int V, int* __restrict__ status, float scale) {
     ce_pdl_begin();
     int t = blockIdx.x;
     int tok = tokens[t];
@@ -23,17 +23,17 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
     }
     const T* row = table + (size_t)tok * H;
 #pragma unroll 4
-    for (int j = threadIdx.x; j < H; j += blockDim.x) x[(size_t)t * H + j] = CeType<T>::load(row + j);
+    for (int j = threadIdx.x; j < H; j += blockDim.x) x[(size_t)t * H + j] = CeType<T>::load(row + j) * scale;
 }
 
 extern "C" int ce_embed(const void* table, int dtype, const int* tokens, float* x, int T, int H, int V,
-                        int* status, cudaStream_t stream) {
+                        int* status, float scale, cudaStream_t stream) {
     if (T == 0) return CE_OK;
     if (!table || !tokens || !x || !status) return ce_fail(CE_ERR_ARG, "ce_embed: null pointer");
     if (dtype == CE_F32)
-        { ce_note("embed_kernel"); ce_launch(embed_kernel<float>, T, H >= 1024 ? 1024 : 256, 0, stream, (const float*)table, tokens, x, H, V, status); }
+        { ce_note("embed_kernel"); ce_launch(embed_kernel<float>, T, H >= 1024 ? 1024 : 256, 0, stream, (const float*)table, tokens, x, H, V, status, scale); }
     else if (dtype == CE_BF16)
-        { ce_note("embed_kernel"); ce_launch(embed_kernel<__nv_bfloat16>, T, H >= 1024 ? 1024 : 256, 0, stream, (const __nv_bfloat16*)table, tokens, x, H, V, status); }
+        { ce_note("embed_kernel"); ce_launch(embed_kernel<__nv_bfloat16>, T, H >= 1024 ? 1024 : 256, 0, stream, (const __nv_bfloat16*)table, tokens, x, H, V, status, scale); }
     else
         return ce_fail(CE_ERR_ARG, "ce_embed: unknown dtype %d", dtype);
     return ce_check_launch("ce_embed");
@@ -473,7 +473,7 @@ extern "C" int ce_add_residual(float* x, const void* delta, int dtype, long long
 // SwiGLU: out[t, i] = silu(gu[t, i]) * gu[t, I + i], silu(z) = z / (1 + exp(-z))
 // (src/model/layers.rs:568, 625-648)
 // ---------------------------------------------------------------------------------------------
-template <typename T>
+template <typename T, bool RELU>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total) {
     ce_pdl_begin();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -482,22 +482,34 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
         size_t t = i / I, c = i - t * I;
         float g = CeType<T>::load(gu + t * 2 * I + c);
         float u = CeType<T>::load(gu + t * 2 * I + I + c);
-        CeType<T>::store(out + i, g / (1.0f + expf(-g)) * u);
+        CeType<T>::store(out + i, RELU ? fmaxf(g, 0.f) * u : g / (1.0f + expf(-g)) * u);
     }
 }
 
-extern "C" int ce_swiglu(const void* gu, void* out, int dtype, int T, int I, cudaStream_t stream) {
+// relu != 0: out = relu(gate) * up instead
+static int gated_act(const void* gu, void* out, int dtype, int T, int I, int relu, cudaStream_t stream) {
     size_t total = (size_t)T * I;
     if (total == 0) return CE_OK;
     if (!gu || !out) return ce_fail(CE_ERR_ARG, "ce_swiglu: null pointer");
     int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
-    if (dtype == CE_F32)
-        { ce_note("swiglu_kernel"); ce_launch(swiglu_kernel<float>, blocks, 256, 0, stream, (const float*)gu, (float*)out, I, total); }
-    else if (dtype == CE_BF16)
-        { ce_note("swiglu_kernel"); ce_launch(swiglu_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, I, total); }
-    else
+    ce_note("swiglu_kernel");
+    if (dtype == CE_F32) {
+        if (relu) ce_launch(swiglu_kernel<float, true>, blocks, 256, 0, stream, (const float*)gu, (float*)out, I, total);
+        else ce_launch(swiglu_kernel<float, false>, blocks, 256, 0, stream, (const float*)gu, (float*)out, I, total);
+    } else if (dtype == CE_BF16) {
+        if (relu) ce_launch(swiglu_kernel<__nv_bfloat16, true>, blocks, 256, 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, I, total);
+        else ce_launch(swiglu_kernel<__nv_bfloat16, false>, blocks, 256, 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, I, total);
+    } else
         return ce_fail(CE_ERR_ARG, "ce_swiglu: unknown dtype %d", dtype);
     return ce_check_launch("ce_swiglu");
+}
+
+extern "C" int ce_reluglu(const void* gu, void* out, int dtype, int T, int I, cudaStream_t stream) {
+    return gated_act(gu, out, dtype, T, I, 1, stream);
+}
+
+extern "C" int ce_swiglu(const void* gu, void* out, int dtype, int T, int I, cudaStream_t stream) {
+    return gated_act(gu, out, dtype, T, I, 0, stream);
 }
 
 // ---------------------------------------------------------------------------------------------

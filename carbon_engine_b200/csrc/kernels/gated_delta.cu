@@ -1,0 +1,334 @@
+// The gated delta rule with a decay per head and key channel: a recurrent mixer whose per-head state S [d, dv]
+// (key channel x value channel, float32) is carried from token to token:
+//
+//     S <- diag(g_t) S;    u_t = beta_t (v_t - S^T k_t);    S <- S + k_t u_t^T;    o_t = S^T q_t
+//
+// (the read-out sees the token's own write).  q, k and v come out of a short causal convolution over time per channel
+// followed by SiLU; q and k are then brought to unit length per head (q also times d^-1/2); the decay is
+// g_t = exp(-exp(A_h) softplus(z_t + bias)) with z_t the token's decay logits (a product of their own);
+// beta_t = sigmoid of a projection, one per head.  Query/key head of value head h: h / (H / G).  Afterwards every
+// head's o_t is divided by its root mean square, multiplied by a weight of size dv and by sigmoid(gate logits).
+//
+// Four kernels, all float32:
+//   prepare     every token on its own: convolution (the inputs before a portion's first token come from the
+//               request's kept rows), SiLU, unit q and k, decay, beta                       (parallel over tokens)
+//   keep        the last taps-1 convolution inputs of every sequence go to its kept rows   (parallel over channels)
+//   walk        one block per (head, sequence, slice of value channels) walks the sequence's tokens of this step
+//               in order, from the state its slot holds, and stores the state back           (the recurrence)
+//   finish      every (token, head): root mean square, weight, gate, one rounding at the store   (parallel)
+//
+// The columns of S (value channels) are independent of one another, so a slice of GD_COLS columns is a block of
+// its own and a column lives in the registers of GD_R neighbouring lanes; the two sums over rows a token needs
+// are a per-thread run plus a butterfly over those lanes: the order of every sum depends on d only, never on
+// how the tokens were cut into steps or on the batch.
+#include "common.cuh"
+
+#define GD_R 16                  // lanes that share a column of the state
+#define GD_COLS 8                // value channels a block walks
+#define GD_TILE 16               // tokens a buffer holds (at most GD_R: lane g of a column stores token g's output)
+
+__device__ __forceinline__ float gd_sigmoid(float z) { return 1.0f / (1.0f + expf(-z)); }
+__device__ __forceinline__ float gd_softplus(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+
+struct GatedDeltaArgs {
+    const float* proj;           // [T, ld]: the convolution's inputs q | k | v from off_conv (C = 2 G d + H dv columns), beta logits at off_b
+    const float* dec;            // [T, H*d] decay logits before the bias
+    const float* gz;             // [T, H*dv] gate logits
+    const float* taps;           // [C, K] convolution weights, the last column the current token's
+    const float* a_log;          // [H]
+    const float* dt_bias;        // [H*d]
+    const float* norm_w;         // [dv]
+    float* prep;                 // [T, P]: q (G d) | k (G d) | v (H dv) | decay (H d) | beta (H); P padded to a multiple of 4
+    float* raw;                  // [T, H*dv] o_t before the norm
+    float* state;                // [slots, H, d, dv]
+    float* kept;                 // [slots, K-1, C] the convolution inputs of the last K-1 tokens, oldest first
+    void* out;                   // [T, H*dv]
+    const int* seq_of_token;
+    const int* seq_slot;
+    const int* q_start;
+    int ld, off_conv, off_b, H, G, d, dv, K, P;
+    float eps;
+};
+
+// One block per token.  A warp per head of q, of k (unit vectors) and of v in turn; then the decays and beta.
+__global__ void gated_delta_prepare_kernel(GatedDeltaArgs a) {
+    ce_pdl_begin();
+    int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    int d = a.d, dv = a.dv, G = a.G, H = a.H, K = a.K;
+    int C = 2 * G * d + H * dv;
+    int b = a.seq_of_token[t];
+    int rel = t - a.q_start[b];                     // tokens of the same sequence before this one in the step
+    const float* kept = a.kept + (size_t)a.seq_slot[b] * (K - 1) * C;
+    float* pw = a.prep + (size_t)t * a.P;
+    float q_scale = rsqrtf((float)d);
+    // convolution + SiLU of channel c at this token
+    auto conv = [&](int c) -> float {
+        float y = 0.f;
+        for (int j = 0; j < K; ++j) {
+            int back = K - 1 - j;                   // how many tokens before this one
+            float x = back <= rel ? a.proj[(size_t)(t - back) * a.ld + a.off_conv + c]
+                                  : kept[(size_t)(K - 1 + rel - back) * C + c];
+            y = fmaf(a.taps[(size_t)c * K + j], x, y);
+        }
+        return y / (1.0f + expf(-y));
+    };
+    int heads = 2 * G + H;
+    for (int hh = warp; hh < heads; hh += nwarp) {
+        bool is_v = hh >= 2 * G;
+        int size = is_v ? dv : d;
+        int c0 = is_v ? 2 * G * d + (hh - 2 * G) * dv : hh * d;
+        if (is_v) {
+            for (int c = lane; c < size; c += 32) pw[c0 + c] = conv(c0 + c);
+            continue;
+        }
+        float ss = 0.f;
+        for (int c = lane; c < size; c += 32) {
+            float y = conv(c0 + c);
+            pw[c0 + c] = y;
+            ss = fmaf(y, y, ss);
+        }
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        float inv = 1.0f / sqrtf(ss + 1e-6f) * (hh < G ? q_scale : 1.0f);
+        __syncwarp();
+        for (int c = lane; c < size; c += 32) pw[c0 + c] *= inv;
+    }
+    float* decay = pw + C;
+    for (int e = threadIdx.x; e < H * d; e += blockDim.x)
+        decay[e] = expf(-expf(a.a_log[e / d]) * gd_softplus(a.dec[(size_t)t * H * d + e] + a.dt_bias[e]));
+    for (int h = threadIdx.x; h < H; h += blockDim.x) decay[H * d + h] = gd_sigmoid(a.proj[(size_t)t * a.ld + a.off_b + h]);
+}
+
+// One thread per (sequence, channel): the kept rows move up by the portion's length and take the portion's last inputs.
+__global__ void gated_delta_keep_kernel(GatedDeltaArgs a, int B) {
+    ce_pdl_begin();
+    int C = 2 * a.G * a.d + a.H * a.dv, K = a.K;
+    size_t total = (size_t)B * C;
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
+        int b = (int)(e / C), c = (int)(e % C);
+        int t0 = a.q_start[b], n = a.q_start[b + 1] - t0;
+        float* kept = a.kept + (size_t)a.seq_slot[b] * (K - 1) * C + c;
+        for (int j = 0; j < K - 1; ++j) {           // ascending: row j + n is read before it is overwritten
+            int rel = n - (K - 1) + j;
+            kept[(size_t)j * C] = rel >= 0 ? a.proj[(size_t)(t0 + rel) * a.ld + a.off_conv + c] : kept[(size_t)(j + n) * C];
+        }
+    }
+}
+
+__device__ __forceinline__ void gd_cp4(float* dst, const float* src) {
+    unsigned s = (unsigned)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(s), "l"(src));
+}
+__device__ __forceinline__ void gd_cp16(float* dst, const float* src) {
+    unsigned s = (unsigned)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(src));
+}
+
+// Copies of one tile of tokens into a buffer: three vectors of d per token (decay, key, query; rows padded to DP floats),
+// GD_COLS values and beta.
+template <int DP, bool VEC>
+__device__ __forceinline__ void gd_stage(const GatedDeltaArgs& a, float* buf, int t0, int n_tok, int h, int col0, int ncols) {
+    int d = a.d, G = a.G, H = a.H, tid = threadIdx.x, nthr = blockDim.x;
+    int g = h / (H / G);
+    int C = 2 * G * d + H * a.dv;
+    int offs[3] = {C + h * d, G * d + g * d, g * d};          // decay, key, query within a prep row
+    float* vbuf = buf + 3 * GD_TILE * DP;
+    if (VEC) {
+        constexpr int DP4 = DP / 4;
+        for (int e = tid; e < 3 * GD_TILE * DP4; e += nthr) {
+            int which = e / (GD_TILE * DP4), tok = (e / DP4) % GD_TILE, c = (e % DP4) * 4;
+            if (tok < n_tok && c < d) gd_cp16(buf + (which * GD_TILE + tok) * DP + c, a.prep + (size_t)(t0 + tok) * a.P + offs[which] + c);
+        }
+    } else {
+        for (int e = tid; e < 3 * GD_TILE * DP; e += nthr) {
+            int which = e / (GD_TILE * DP), tok = (e / DP) % GD_TILE, c = e % DP;
+            if (tok < n_tok && c < d) gd_cp4(buf + (which * GD_TILE + tok) * DP + c, a.prep + (size_t)(t0 + tok) * a.P + offs[which] + c);
+        }
+    }
+    for (int e = tid; e < GD_TILE * (GD_COLS + 1); e += nthr) {
+        int tok = e / (GD_COLS + 1), c = e % (GD_COLS + 1);
+        if (tok >= n_tok) continue;
+        const float* row = a.prep + (size_t)(t0 + tok) * a.P;
+        if (c < ncols) gd_cp4(vbuf + tok * (GD_COLS + 1) + c, row + 2 * G * d + h * a.dv + col0 + c);
+        else if (c == GD_COLS) gd_cp4(vbuf + tok * (GD_COLS + 1) + c, row + C + H * d + h);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+}
+
+template <int RPT, bool VEC>
+__global__ void __launch_bounds__(GD_R * GD_COLS) gated_delta_walk_kernel(GatedDeltaArgs a) {
+    ce_pdl_begin();
+    extern __shared__ __align__(16) float gd_smem[];
+    int d = a.d, dv = a.dv;
+    int h = blockIdx.x, b = blockIdx.y, col0 = blockIdx.z * GD_COLS, tid = threadIdx.x;
+    int t_begin = a.q_start[b], t_end = a.q_start[b + 1];
+    if (t_end <= t_begin) return;
+    int ncols = min(GD_COLS, dv - col0);
+    int jj = tid / GD_R, g = tid % GD_R, j = col0 + jj;
+    int i0 = g * RPT;                         // this thread's rows: i0 .. i0 + RPT - 1 (RPT is a multiple of 4)
+    bool owner = jj < ncols;
+    float* sp = a.state + ((size_t)a.seq_slot[b] * a.H + h) * d * dv;
+    float S[RPT];
+#pragma unroll
+    for (int m = 0; m < RPT; ++m) S[m] = (owner && i0 + m < d) ? sp[(size_t)(i0 + m) * dv + j] : 0.f;
+    // a row of the staged vectors is padded to GD_R * RPT floats, so that every thread reads whole float4
+    constexpr int dp = GD_R * RPT;
+    int buf_floats = 3 * GD_TILE * dp + GD_TILE * (GD_COLS + 1);
+    buf_floats = (buf_floats + 3) / 4 * 4;
+    for (int e = tid; e < 2 * buf_floats; e += blockDim.x) gd_smem[e] = 0.f;       // the padding stays zero
+    __syncthreads();
+    int n_tiles = (t_end - t_begin + GD_TILE - 1) / GD_TILE;
+    gd_stage<dp, VEC>(a, gd_smem, t_begin, min(GD_TILE, t_end - t_begin), h, col0, ncols);
+    for (int tile = 0; tile < n_tiles; ++tile) {
+        int t0 = t_begin + tile * GD_TILE, n_tok = min(GD_TILE, t_end - t0);
+        float* buf = gd_smem + (tile & 1) * buf_floats;
+        if (tile + 1 < n_tiles) {
+            gd_stage<dp, VEC>(a, gd_smem + ((tile + 1) & 1) * buf_floats, t0 + GD_TILE, min(GD_TILE, t_end - t0 - GD_TILE), h, col0, ncols);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();
+        const float* vbuf = buf + 3 * GD_TILE * dp;
+        // The sum over rows of S^T q is not needed by the next token: every thread keeps its part for each token of
+        // the tile, and the butterflies of all tokens run together after the walk (their latencies overlap).
+        float part[GD_TILE];
+#pragma unroll
+        for (int tok = 0; tok < GD_TILE; ++tok) {
+            part[tok] = 0.f;
+            if (tok < n_tok) {
+                const float4* w_ = reinterpret_cast<const float4*>(buf + (0 * GD_TILE + tok) * dp + i0);
+                const float4* k_ = reinterpret_cast<const float4*>(buf + (1 * GD_TILE + tok) * dp + i0);
+                const float4* q_ = reinterpret_cast<const float4*>(buf + (2 * GD_TILE + tok) * dp + i0);
+                // the decay, and k^T (decayed S) over this thread's rows in four runs (a fixed order)
+                float p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;
+#pragma unroll
+                for (int m = 0; m < RPT / 4; ++m) {
+                    float4 w = w_[m], k = k_[m];
+                    S[4 * m] *= w.x; S[4 * m + 1] *= w.y; S[4 * m + 2] *= w.z; S[4 * m + 3] *= w.w;
+                    p0 = fmaf(k.x, S[4 * m], p0); p1 = fmaf(k.y, S[4 * m + 1], p1);
+                    p2 = fmaf(k.z, S[4 * m + 2], p2); p3 = fmaf(k.w, S[4 * m + 3], p3);
+                }
+                float dot = (p0 + p1) + (p2 + p3);
+                // over the column's sixteen lanes in two rounds of four: every lane adds the same pairs, so all hold the same sum
+                {
+                    float e1 = __shfl_xor_sync(0xffffffffu, dot, 1), e2 = __shfl_xor_sync(0xffffffffu, dot, 2),
+                          e3 = __shfl_xor_sync(0xffffffffu, dot, 3);
+                    dot = (dot + e1) + (e2 + e3);
+                    float f1 = __shfl_xor_sync(0xffffffffu, dot, 4), f2 = __shfl_xor_sync(0xffffffffu, dot, 8),
+                          f3 = __shfl_xor_sync(0xffffffffu, dot, 12);
+                    dot = (dot + f1) + (f2 + f3);
+                }
+                float vj = owner ? vbuf[tok * (GD_COLS + 1) + jj] : 0.f;
+                float u = vbuf[tok * (GD_COLS + 1) + GD_COLS] * (vj - dot);
+                float q0 = 0.f, q1 = 0.f, q2 = 0.f, q3 = 0.f;
+#pragma unroll
+                for (int m = 0; m < RPT / 4; ++m) {
+                    float4 k = k_[m], q = q_[m];
+                    float s0 = fmaf(k.x, u, S[4 * m]), s1 = fmaf(k.y, u, S[4 * m + 1]);
+                    float s2 = fmaf(k.z, u, S[4 * m + 2]), s3 = fmaf(k.w, u, S[4 * m + 3]);
+                    S[4 * m] = s0; S[4 * m + 1] = s1; S[4 * m + 2] = s2; S[4 * m + 3] = s3;
+                    q0 = fmaf(s0, q.x, q0); q1 = fmaf(s1, q.y, q1); q2 = fmaf(s2, q.z, q2); q3 = fmaf(s3, q.w, q3);
+                }
+                part[tok] = (q0 + q1) + (q2 + q3);
+            }
+        }
+#pragma unroll
+        for (int o = 1; o < GD_R; o <<= 1)
+#pragma unroll
+            for (int tok = 0; tok < GD_TILE; ++tok) part[tok] += __shfl_xor_sync(0xffffffffu, part[tok], o);
+        // lane g of a column stores token g of the tile (GD_TILE <= GD_R)
+        float mine = part[0];
+#pragma unroll
+        for (int tok = 1; tok < GD_TILE; ++tok) mine = g == tok ? part[tok] : mine;
+        if (owner && g < n_tok) a.raw[(size_t)(t0 + g) * a.H * dv + h * dv + j] = mine;
+        __syncthreads();             // the buffer is free for the tile after the next
+    }
+#pragma unroll
+    for (int m = 0; m < RPT; ++m)
+        if (owner && i0 + m < d) sp[(size_t)(i0 + m) * dv + j] = S[m];
+}
+
+// One block per token, a warp per head in turn: root mean square over the head's values, weight, gate.
+template <typename T>
+__global__ void gated_delta_finish_kernel(GatedDeltaArgs a) {
+    ce_pdl_begin();
+    int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    int dv = a.dv, n = a.H * dv;
+    const float* o = a.raw + (size_t)t * n;
+    const float* gz = a.gz + (size_t)t * n;
+    for (int h = warp; h < a.H; h += nwarp) {
+        float ss = 0.f;
+        for (int c = lane; c < dv; c += 32) ss = fmaf(o[h * dv + c], o[h * dv + c], ss);
+        for (int k = 16; k > 0; k >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, k);
+        float inv = 1.0f / sqrtf(ss / (float)dv + a.eps);
+        for (int c = lane; c < dv; c += 32) {
+            int col = h * dv + c;
+            CeType<T>::store((T*)a.out + (size_t)t * n + col, o[col] * inv * a.norm_w[c] * gd_sigmoid(gz[col]));
+        }
+    }
+}
+
+template <int RPT>
+static void gd_launch_walk(const GatedDeltaArgs& a, int B, bool vec, cudaStream_t stream) {
+    size_t floats = 3 * GD_TILE * GD_R * RPT + GD_TILE * (GD_COLS + 1);
+    size_t smem = (size_t)2 * ((floats + 3) / 4 * 4) * sizeof(float);
+    dim3 grid(a.H, B, (a.dv + GD_COLS - 1) / GD_COLS);
+    ce_note("gated_delta_walk_kernel");
+    if (vec) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(gated_delta_walk_kernel<RPT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        ce_launch(gated_delta_walk_kernel<RPT, true>, grid, GD_R * GD_COLS, smem, stream, a);
+    } else {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(gated_delta_walk_kernel<RPT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        ce_launch(gated_delta_walk_kernel<RPT, false>, grid, GD_R * GD_COLS, smem, stream, a);
+    }
+}
+
+// Floats of a ``prep`` row for these sizes.
+extern "C" int ce_gated_delta_prep_width(int H, int G, int d, int dv) {
+    return (2 * G * d + H * dv + H * d + H + 3) / 4 * 4;
+}
+
+// stage: 1 prepare, 2 keep, 3 walk, 4 finish (each one launch, so that each is counted and timed by itself)
+extern "C" int ce_gated_delta(const float* proj, const float* dec, const float* gz, const float* taps, const float* a_log,
+                              const float* dt_bias, const float* norm_w, float* prep, float* raw, float* state, float* kept,
+                              void* out, int out_dtype, const int* seq_of_token, const int* seq_slot, const int* q_start,
+                              int T, int B, int ld, int off_conv, int off_b, int H, int G, int d, int dv, int K, float eps,
+                              int stage, cudaStream_t stream) {
+    if (B == 0 || T == 0) return CE_OK;
+    if (stage < 1 || stage > 4) return ce_fail(CE_ERR_ARG, "ce_gated_delta: stage %d", stage);
+    if (!proj || !dec || !gz || !taps || !a_log || !dt_bias || !norm_w || !prep || !raw || !state || !out || !seq_of_token ||
+        !seq_slot || !q_start || (K > 1 && !kept))
+        return ce_fail(CE_ERR_ARG, "ce_gated_delta: null pointer");
+    if (d <= 0 || d > 256 || dv <= 0) return ce_fail(CE_ERR_SIZE, "ce_gated_delta: head sizes %d / %d (keys up to 256)", d, dv);
+    if (H <= 0 || G <= 0 || H % G || B > 65535 || K < 1 || K > 64)
+        return ce_fail(CE_ERR_SIZE, "ce_gated_delta: %d heads, %d key heads, %d sequences, %d taps", H, G, B, K);
+    if (out_dtype != CE_F32 && out_dtype != CE_BF16) return ce_fail(CE_ERR_ARG, "ce_gated_delta: unknown dtype %d", out_dtype);
+    int P = ce_gated_delta_prep_width(H, G, d, dv);
+    GatedDeltaArgs a{proj, dec, gz, taps, a_log, dt_bias, norm_w, prep, raw, state, kept, out, seq_of_token, seq_slot, q_start,
+                     ld, off_conv, off_b, H, G, d, dv, K, P, eps};
+    int heads = 2 * G + H;
+    int threads = heads >= 8 ? 256 : 32 * heads;
+    if (stage == 1) {
+        ce_note("gated_delta_prepare_kernel");
+        ce_launch(gated_delta_prepare_kernel, T, threads, 0, stream, a);
+    } else if (stage == 2) {
+        if (K == 1) return CE_OK;
+        size_t total = (size_t)B * (2 * G * d + H * dv), want = (total + 255) / 256;
+        ce_note("gated_delta_keep_kernel");
+        ce_launch(gated_delta_keep_kernel, (int)(want < 148 * 8 ? want : 148 * 8), 256, 0, stream, a, B);
+    } else if (stage == 4) {
+        ce_note("gated_delta_finish_kernel");
+        int th = H >= 8 ? 256 : 32 * H;
+        if (out_dtype == CE_F32) ce_launch(gated_delta_finish_kernel<float>, T, th, 0, stream, a);
+        else ce_launch(gated_delta_finish_kernel<__nv_bfloat16>, T, th, 0, stream, a);
+    } else {
+        // 16-byte copies where every source address is a multiple of 16
+        int C = 2 * G * d + H * dv;
+        bool vec = d % 4 == 0 && C % 4 == 0 && ((uintptr_t)prep & 15) == 0;
+        int rpt = (d + GD_R - 1) / GD_R;
+        if (rpt <= 4) gd_launch_walk<4>(a, B, vec, stream);
+        else if (rpt <= 8) gd_launch_walk<8>(a, B, vec, stream);
+        else gd_launch_walk<16>(a, B, vec, stream);
+    }
+    return ce_check_launch("ce_gated_delta");
+}

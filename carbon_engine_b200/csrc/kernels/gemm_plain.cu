@@ -8,20 +8,20 @@
 //
 // Epilogues: store (in the activation dtype or float32), add into the float32 residual stream, or
 // SwiGLU, where W holds the gate rows [0, N) and the up rows [N, 2N) and the output is
-// silu(gate) * up (src/model/layers.rs:625-648).
+// silu(gate) * up (src/model/layers.rs:625-648), or relu(gate) * up.
 #include "common.cuh"
 
 #define GP_BM 64
 #define GP_BN 64
 #define GP_BK 16
 
-enum { GP_STORE = 0, GP_STORE_F32 = 1, GP_ACCUM_F32 = 2, GP_SWIGLU = 3 };
+enum { GP_STORE = 0, GP_STORE_F32 = 1, GP_ACCUM_F32 = 2, GP_SWIGLU = 3, GP_RELUGLU = 4 };     // 4: relu(gate) * up
 
 template <typename T, int MODE>
 __global__ void __launch_bounds__(256) gemm_plain_kernel(const T* __restrict__ A, const T* __restrict__ W,
                                                          void* __restrict__ Cv, int M, int N, int K, int lda, int ldc) {
     ce_pdl_begin();
-    constexpr int NW = MODE == GP_SWIGLU ? 2 : 1;
+    constexpr int NW = (MODE == GP_SWIGLU || MODE == GP_RELUGLU) ? 2 : 1;
     __shared__ float As[GP_BK][GP_BM + 1];
     __shared__ float Ws[NW][GP_BK][GP_BN + 1];
     int tid = threadIdx.x;
@@ -79,6 +79,8 @@ __global__ void __launch_bounds__(256) gemm_plain_kernel(const T* __restrict__ A
                 ((float*)Cv)[o] = acc[0][i][j];
             } else if (MODE == GP_ACCUM_F32) {
                 ((float*)Cv)[o] += acc[0][i][j];
+            } else if (MODE == GP_RELUGLU) {
+                CeType<T>::store((T*)Cv + o, fmaxf(acc[0][i][j], 0.f) * acc[NW - 1][i][j]);
             } else {
                 float g = acc[0][i][j], u = acc[NW - 1][i][j];
                 CeType<T>::store((T*)Cv + o, g / (1.0f + expf(-g)) * u);
@@ -96,6 +98,7 @@ static int launch_plain(const void* A, const void* W, void* C, int M, int N, int
         case GP_STORE_F32: { ce_note("gemm_plain_kernel"); ce_launch(gemm_plain_kernel<T, GP_STORE_F32>, grid, 256, 0, stream, (const T*)A, (const T*)W, C, M, N, K, lda, ldc); } break;
         case GP_ACCUM_F32: { ce_note("gemm_plain_kernel"); ce_launch(gemm_plain_kernel<T, GP_ACCUM_F32>, grid, 256, 0, stream, (const T*)A, (const T*)W, C, M, N, K, lda, ldc); } break;
         case GP_SWIGLU: { ce_note("gemm_plain_kernel"); ce_launch(gemm_plain_kernel<T, GP_SWIGLU>, grid, 256, 0, stream, (const T*)A, (const T*)W, C, M, N, K, lda, ldc); } break;
+        case GP_RELUGLU: { ce_note("gemm_plain_kernel"); ce_launch(gemm_plain_kernel<T, GP_RELUGLU>, grid, 256, 0, stream, (const T*)A, (const T*)W, C, M, N, K, lda, ldc); } break;
         default: return ce_fail(CE_ERR_ARG, "ce_gemm_plain: unknown epilogue %d", mode);
     }
     return ce_check_launch("ce_gemm_plain");

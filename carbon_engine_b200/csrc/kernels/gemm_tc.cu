@@ -38,7 +38,8 @@ constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;
 constexpr uint32_t SPIN_LIMIT = 1u << 20;     // with the back-off below: about a second at most
 
-enum { TC_STORE = 0, TC_STORE_F32 = 1, TC_ACCUM_F32 = 2, TC_SWIGLU = 3 };
+enum { TC_STORE = 0, TC_STORE_F32 = 1, TC_ACCUM_F32 = 2, TC_SWIGLU = 3, TC_RELUGLU = 4 };     // 4: relu(gate) * up, laid out and tiled like 3
+#define TC_GATED(mode) ((mode) == TC_SWIGLU || (mode) == TC_RELUGLU)
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -139,13 +140,16 @@ struct TcArgs {
 __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + __expf(-g)) * u; }
 // the same with the approximate reciprocal (the result is rounded to bfloat16 right after)
 __device__ __forceinline__ float silu_mul_fast(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
+// the gated epilogue's activation by mode
+__device__ __forceinline__ float gated_mul(int mode, float g, float u) { return mode == TC_RELUGLU ? fmaxf(g, 0.f) * u : silu_mul(g, u); }
+__device__ __forceinline__ float gated_mul_fast(int mode, float g, float u) { return mode == TC_RELUGLU ? fmaxf(g, 0.f) * u : silu_mul_fast(g, u); }
 
 __device__ __forceinline__ void epilogue_store(const TcArgs& a, int m, int n, float v, float up) {
     size_t o = (size_t)m * a.ldo + n;
     if (a.mode == TC_STORE) ((__nv_bfloat16*)a.out)[o] = __float2bfloat16_rn(v);
     else if (a.mode == TC_STORE_F32) ((float*)a.out)[o] = v;
     else if (a.mode == TC_ACCUM_F32) ((float*)a.out)[o] += v;
-    else ((__nv_bfloat16*)a.out)[o] = __float2bfloat16_rn(silu_mul(v, up));
+    else ((__nv_bfloat16*)a.out)[o] = __float2bfloat16_rn(gated_mul(a.mode, v, up));
 }
 
 template <int BN, int NACC, bool COOP>
@@ -322,7 +326,7 @@ __global__ void __launch_bounds__(THREADS, 2) gemm_tc_kernel(const __grid_consta
                     for (int j = 0; j < 8; ++j) {
                         float gate = up_row ? xg[j] : g[j];
                         float upv = up_row ? g[8 + j] : xu[j];
-                        if (c + t0 + j < m_valid) op[(size_t)j * a.ldo] = __float2bfloat16_rn(silu_mul_fast(gate, upv));
+                        if (c + t0 + j < m_valid) op[(size_t)j * a.ldo] = __float2bfloat16_rn(gated_mul_fast(a.mode, gate, upv));
                     }
                 }
             }
@@ -933,7 +937,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_pair_kernel(const __grid_cons
                         for (int j = 0; j < 16; ++j) {
                             float gate = up_row ? xg[j] : g[j];
                             float upv = up_row ? g[16 + j] : xu[j];
-                            if (c + t0 + j < m_valid) op[(size_t)j * a.ldo] = __float2bfloat16_rn(silu_mul_fast(gate, upv));
+                            if (c + t0 + j < m_valid) op[(size_t)j * a.ldo] = __float2bfloat16_rn(gated_mul_fast(a.mode, gate, upv));
                         }
                     }
                     continue;
@@ -1134,7 +1138,7 @@ extern "C" int ce_gemm_tc_tile_tokens(int M) {
 // Scratch floats a product needs (0 without split-K).
 extern "C" long long ce_gemm_tc_scratch(int M, int N, int K, int mode) {
     int s = ce_gemm_tc_splits(M, N, K);
-    if (s == 1 || mode == TC_SWIGLU) return 0;         // (the SwiGLU product never splits K)
+    if (s == 1 || TC_GATED(mode)) return 0;         // (the SwiGLU product never splits K)
     int bn = ce_gemm_tc_tile_tokens(M);
     long long tiles = (long long)((N + BM - 1) / BM) * ((M + bn - 1) / bn);
     return (long long)s * tiles * bn * BM;
@@ -1154,8 +1158,8 @@ extern "C" int ce_gemm_tc(const void* A, const void* W, void* C, int M, int N, i
     if (!ce_gemm_tc_supported(M, N, K, lda))
         return ce_fail(CE_ERR_SIZE, "ce_gemm_tc: K=%d and the row stride %d must be multiples of 8", K, lda);
     if (((uintptr_t)A | (uintptr_t)W) & 15) return ce_fail(CE_ERR_SIZE, "ce_gemm_tc: operands must be 16-byte aligned");
-    if (mode < 0 || mode > 3) return ce_fail(CE_ERR_ARG, "ce_gemm_tc: unknown epilogue %d", mode);
-    int nacc = mode == TC_SWIGLU ? 2 : 1;
+    if (mode < 0 || mode > 4) return ce_fail(CE_ERR_ARG, "ce_gemm_tc: unknown epilogue %d", mode);
+    int nacc = TC_GATED(mode) ? 2 : 1;
     int kblocks = (K + BK - 1) / BK;
     bool early_pairs = pairs_from_129(M, N, nacc);
     if (M > 256 || early_pairs) {       // many tokens: the persistent kernels, no split-K

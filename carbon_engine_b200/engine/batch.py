@@ -100,6 +100,8 @@ class StepContext:
         self.bufs = bufs
         #: what each kind of mixer laid out for this step (``Mixer.plan_step``), by the mixer's ``plan_key``
         self.plans: Dict[str, Any] = {}
+        #: what a layer leaves for later layers of the SAME step (values that later layers blend with their own), by name
+        self.shared: Dict[str, Any] = {}
         self._scratch = {}
         self.n_decode = 0                    # the first n_decode sequences bring exactly one token
         self.max_position = 0

@@ -14,7 +14,9 @@ import torch
 from .csrc.kernel_lib import KernelError, kernels
 
 F32, BF16 = 0, 1
-GEMM_STORE, GEMM_STORE_F32, GEMM_ACCUM_F32, GEMM_SWIGLU = 0, 1, 2, 3
+GEMM_STORE, GEMM_STORE_F32, GEMM_ACCUM_F32, GEMM_SWIGLU, GEMM_RELUGLU = 0, 1, 2, 3, 4
+#: epilogues whose weight holds gate rows and up rows: act(gate) * up with act = SiLU or ReLU
+GEMM_GATED = (GEMM_SWIGLU, GEMM_RELUGLU)
 ROPE_PAIRINGS = {"half": 0, "interleaved": 1}
 
 
@@ -176,12 +178,12 @@ def reset_kernel_counts() -> None:
     kernels().ce_kernel_counts_reset()
 
 
-def embed(table: torch.Tensor, tokens: torch.Tensor, x: torch.Tensor, status: torch.Tensor) -> None:
-    """x[t, :] = table[tokens[t], :] as float32."""
+def embed(table: torch.Tensor, tokens: torch.Tensor, x: torch.Tensor, status: torch.Tensor, scale: float = 1.0) -> None:
+    """x[t, :] = table[tokens[t], :] * scale as float32."""
     _need(table, "table"); _need(tokens, "tokens", torch.int32); _need(x, "x", torch.float32)
     T, H = x.shape
     _ok(kernels().ce_embed(_ptr(table), dtype_code(table.dtype), _ptr(tokens), _ptr(x), T, H, table.shape[0],
-                           _ptr(status), _stream()))
+                           _ptr(status), float(scale), _stream()))
 
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float,
@@ -242,6 +244,178 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
     _ok(kernels().ce_swiglu(_ptr(gate_up), _ptr(out), dtype_code(out.dtype), T, I, _stream()))
 
 
+def reluglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, i] = relu(gate_up[t, i]) * gate_up[t, I + i]."""
+    _need(gate_up, "gate_up"); _need(out, "out", gate_up.dtype)
+    T, I = out.shape
+    if gate_up.shape != (T, 2 * I):
+        raise KernelError("reluglu: gate_up must be [T, 2I]")
+    _ok(kernels().ce_reluglu(_ptr(gate_up), _ptr(out), dtype_code(out.dtype), T, I, _stream()))
+
+
+def layernorm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, out: torch.Tensor, eps: float,
+              rows: Optional[torch.Tensor] = None) -> None:
+    """out[r] = (x - mean) / sqrt(var + eps) * weight + bias of row rows[r] (or r); x float32."""
+    _need(x, "x", torch.float32); _need(weight, "weight", torch.float32); _need(bias, "bias", torch.float32); _need(out, "out")
+    R, H = out.shape
+    if x.shape[1] != H or weight.numel() != H or bias.numel() != H:
+        raise KernelError(f"layernorm: widths differ: x {tuple(x.shape)}, weight {tuple(weight.shape)}, out {tuple(out.shape)}")
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+    _ok(kernels().ce_layernorm(_ptr(x), _ptr(weight), _ptr(bias), _ptr(out), dtype_code(out.dtype), _ptr(rows), R, H, float(eps),
+                               _stream()))
+
+
+def rmsnorm_add(y: torch.Tensor, weight: torch.Tensor, x: torch.Tensor, eps: float) -> None:
+    """x[t] += y[t] / sqrt(mean(y[t]^2) + eps) * weight; all float32."""
+    _need(y, "y", torch.float32); _need(weight, "weight", torch.float32); _need(x, "x", torch.float32)
+    if y.shape != x.shape or weight.numel() != x.shape[1]:
+        raise KernelError("rmsnorm_add: sizes differ")
+    _ok(kernels().ce_rmsnorm_add(_ptr(y), _ptr(weight), _ptr(x), x.shape[0], x.shape[1], float(eps), _stream()))
+
+
+def tanh_cap(x: torch.Tensor, cap: float) -> None:
+    """x <- cap * tanh(x / cap) in place (float32)."""
+    _need(x, "x", torch.float32)
+    _ok(kernels().ce_tanh_cap(_ptr(x), x.numel(), float(cap), _stream()))
+
+
+def copy_cols(src: torch.Tensor, off: int, width: int, out: torch.Tensor) -> None:
+    """out[t, l] = src[t, off + l] for l < width; src float32 (row stride src.stride(0)), out float32 or bfloat16."""
+    _need(out, "out")
+    if src.dtype != torch.float32 or src.stride(-1) != 1 or not src.is_cuda:
+        raise KernelError("copy_cols: src must be float32 rows on the GPU")
+    if out.shape != (src.shape[0], width) or off + width > src.shape[1]:
+        raise KernelError("copy_cols: sizes do not fit")
+    _ok(kernels().ce_copy_cols(_ptr(src), _ptr(out), dtype_code(out.dtype), src.shape[0], src.stride(0), int(off), int(width),
+                               _stream()))
+
+
+def side_gate(z: torch.Tensor, table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, off: int, status) -> None:
+    """out[t, j] = gelu_tanh(z[t, j]) * table[tokens[t], off + j]; z float32 [T, D], out in the table's dtype."""
+    _need(z, "z", torch.float32); _need(table, "table"); _need(tokens, "tokens", torch.int32); _need(out, "out", table.dtype)
+    T, D = z.shape
+    if out.shape != z.shape:
+        raise KernelError("side_gate: sizes differ")
+    _ok(kernels().ce_side_gate(_ptr(z), _ptr(table), dtype_code(table.dtype), _ptr(tokens), _ptr(out), T, D, table.shape[1],
+                               int(off), table.shape[0], _ptr(status), _stream()))
+
+
+def value_mix(rows: torch.Tensor, off: int, n: int, first: torch.Tensor, first_off: int, lam: float) -> None:
+    """rows[:, off:off+n] <- (1 - lam) rows[:, off:off+n] + lam first[:, first_off:first_off+n], in place."""
+    if rows.dtype != first.dtype or rows.stride(-1) != 1 or first.stride(-1) != 1 or rows.shape[0] != first.shape[0]:
+        raise KernelError("value_mix: the two row sets must agree in dtype and token count")
+    if off + n > rows.shape[1] or first_off + n > first.shape[1]:
+        raise KernelError("value_mix: columns outside a row")
+    _ok(kernels().ce_value_mix(_ptr(rows), dtype_code(rows.dtype), rows.stride(0), int(off), int(n), _ptr(first), first.stride(0),
+                               int(first_off), float(lam), rows.shape[0], _stream()))
+
+
+def latent_prepare(proj, wq, wkv, cq, k_pool, cos, sin, positions, seq_of_token, seq_slot, block_table, status, off_q: int,
+                   qr: int, off_kv: int, r: int, dr: int, rd: int, page_size: int, eps: float, write_kv: bool = True) -> None:
+    """Latent attention's operands from one float32 product row: cq = rms_norm(query latent) * wq; the token's
+    cache row [rms_norm(latent) * wkv | rotated key part] into ``k_pool`` [pages, 1, page, r + dr]."""
+    _need(proj, "proj", torch.float32); _need(wq, "wq", torch.float32); _need(wkv, "wkv", torch.float32); _need(cq, "cq")
+    if cq.shape != (proj.shape[0], qr) or wq.numel() != qr or wkv.numel() != r:
+        raise KernelError("latent_prepare: sizes do not fit")
+    if write_kv:
+        _need(k_pool, "k_pool", cq.dtype)
+        if tuple(k_pool.shape[1:]) != (1, page_size, r + dr):
+            raise KernelError(f"latent_prepare: pool {tuple(k_pool.shape)} is not [pages, 1, {page_size}, {r + dr}]")
+    if rd > 0 and (cos is None or cos.shape[1] != rd // 2):
+        raise KernelError("latent_prepare: rotary table width is not rd / 2")
+    _ok(kernels().ce_latent_prepare(
+        _ptr(proj), _ptr(wq), _ptr(wkv), _ptr(cq), _ptr(k_pool), dtype_code(cq.dtype), _ptr(cos), _ptr(sin), _ptr(positions),
+        _ptr(seq_of_token), _ptr(seq_slot), _ptr(block_table), _ptr(status), proj.shape[0], proj.stride(0), int(off_q), int(qr),
+        int(off_kv), int(r), int(dr), int(rd), int(page_size), block_table.shape[1] if block_table is not None else 0,
+        k_pool.shape[0] if k_pool is not None else 0, cos.shape[0] if cos is not None else 0, 1 if write_kv else 0, float(eps),
+        _stream()))
+
+
+def rope_part(src, src_head: int, src_off: int, dst, dst_head: int, dst_off: int, cos, sin, positions, status, heads: int,
+              dr: int, rd: int) -> None:
+    """dst[t, h*dst_head + dst_off + i] = src[t, h*src_head + src_off + i] for i < dr, its first rd elements rotated in half pairs."""
+    if src.dtype != dst.dtype or src.stride(-1) != 1 or dst.stride(-1) != 1:
+        raise KernelError("rope_part: rows of one dtype are needed")
+    _ok(kernels().ce_rope_part(_ptr(src), src.stride(0), int(src_head), int(src_off), _ptr(dst), dst.stride(0), int(dst_head),
+                               int(dst_off), dtype_code(src.dtype), _ptr(cos), _ptr(sin), _ptr(positions), _ptr(status),
+                               src.shape[0], int(heads), int(dr), int(rd), cos.shape[0] if cos is not None else 0, _stream()))
+
+
+def head_matmul(inp, in_head: int, w, out, out_head: int, heads: int, n: int, k: int, gate=None) -> None:
+    """out[t, h*out_head + j] = sum_i inp[t, h*in_head + i] * w[h, j, i] (j < n, i < k), optionally times
+    sigmoid(gate[t, h*n + j]) (float32 logits); w [heads, n, k] contiguous, operands and output in one dtype."""
+    _need(w, "w", inp.dtype)
+    if tuple(w.shape) != (heads, n, k) or out.dtype != inp.dtype or inp.stride(-1) != 1 or out.stride(-1) != 1:
+        raise KernelError("head_matmul: shapes or dtypes do not fit")
+    if gate is not None and (gate.dtype != torch.float32 or gate.stride(-1) != 1):
+        raise KernelError("head_matmul: the gate logits must be float32 rows")
+    prof = profiling()
+    if prof is not None:
+        M = inp.shape[0]
+        prof.note_work((M * heads * (n + k) + heads * n * k) * inp.element_size(), 2 * M * heads * n * k)
+    _ok(kernels().ce_head_matmul(_ptr(inp), inp.stride(0), int(in_head), _ptr(w), _ptr(out), out.stride(0), int(out_head),
+                                 _ptr(gate), gate.stride(0) if gate is not None else 0, dtype_code(inp.dtype), inp.shape[0],
+                                 int(heads), int(n), int(k), _stream()))
+
+
+def masked_attention(q, q_head: int, k_pool, v_pool, ldk: int, ldv: int, gate, out, positions, seq_of_token, seq_slot,
+                     block_table, status, nh: int, nkv: int, d: int, dv: int, page_size: int, window: int, keep_first: int,
+                     scale: float, softcap: float) -> None:
+    """Softmax attention in float32 arithmetic with separate key and value head sizes, a tanh cap on the scores
+    (0: none), a window (0: none) that keeps the first ``keep_first`` keys visible, and an optional sigmoid gate per
+    output element.  ``v_pool`` may be the key pool itself (``ldv`` = ``ldk``): the values are then the leading
+    ``dv`` elements of every key row."""
+    _need(k_pool, "k_pool"); _need(out, "out", k_pool.dtype)
+    if q.dtype != k_pool.dtype or v_pool.dtype != k_pool.dtype:
+        raise KernelError("masked_attention: q and the cache differ in dtype")
+    _ok(kernels().ce_masked_attention(
+        _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(gate), _ptr(out), dtype_code(out.dtype), _ptr(positions), _ptr(seq_of_token),
+        _ptr(seq_slot), _ptr(block_table), _ptr(status), out.shape[0], nh, nkv, d, dv, q.stride(0), int(q_head), int(ldk), int(ldv),
+        gate.stride(0) if gate is not None else 0, page_size, block_table.shape[1], k_pool.shape[0], int(window), int(keep_first),
+        float(scale), float(softcap), _stream()))
+
+
+def masked_attention_mma_supported(d: int, dv: int, q_stride: int, q_head: int, ldk: int, ldv: int) -> bool:
+    return False
+
+
+def gated_delta_prep_width(heads: int, key_heads: int, d: int, dv: int) -> int:
+    return kernels().ce_gated_delta_prep_width(heads, key_heads, d, dv)
+
+
+def gated_delta(proj, dec, gz, taps, a_log, dt_bias, norm_w, prep, raw, state, kept, out, seq_of_token, seq_slot, q_start,
+                n_seqs: int, off_conv: int, off_b: int, heads: int, key_heads: int, d: int, dv: int, n_taps: int, eps: float) -> None:
+    """The gated delta rule with a decay per key channel over each sequence's tokens of the step, from and to ``state``
+    [slots, heads, d, dv] and the convolution's kept rows ``kept`` [slots, taps - 1, C] (both float32).  ``proj`` float32
+    [T, ld] holds the convolution's inputs q | k | v from ``off_conv`` and the beta logits at ``off_b``; ``dec``
+    [T, heads * d] the decay logits, ``gz`` [T, heads * dv] the gate logits.  Four launches: prepare, keep, walk, finish."""
+    _need(state, "state", torch.float32); _need(out, "out")
+    for name, t in (("dec", dec), ("gz", gz), ("taps", taps), ("a_log", a_log), ("dt_bias", dt_bias), ("norm_w", norm_w),
+                    ("prep", prep), ("raw", raw)):
+        _need(t, name, torch.float32)
+    if proj.dtype != torch.float32 or proj.stride(-1) != 1:
+        raise KernelError("gated_delta: proj must be float32 rows")
+    T, C = out.shape[0], 2 * key_heads * d + heads * dv
+    P = gated_delta_prep_width(heads, key_heads, d, dv)
+    if tuple(state.shape[1:]) != (heads, d, dv) or out.shape[1] != heads * dv or dec.shape != (T, heads * d) or \
+            gz.shape != (T, heads * dv) or prep.numel() < T * P or raw.numel() < T * heads * dv or tuple(taps.shape) != (C, n_taps) or \
+            (n_taps > 1 and tuple(kept.shape[1:]) != (n_taps - 1, C)):
+        raise KernelError("gated_delta: sizes do not fit")
+    prof, work = profiling(), None
+    if prof is not None:
+        work, prof._work = prof._work, (0, 0)            # the caller's figures belong to the walk
+    for stage in (1, 2, 3, 4):
+        if stage == 2 and n_taps == 1:
+            continue
+        if stage == 3 and work is not None:
+            prof.note_work(*work)
+        _ok(kernels().ce_gated_delta(_ptr(proj), _ptr(dec), _ptr(gz), _ptr(taps), _ptr(a_log), _ptr(dt_bias), _ptr(norm_w),
+                                     _ptr(prep), _ptr(raw), _ptr(state), _ptr(kept), _ptr(out), dtype_code(out.dtype),
+                                     _ptr(seq_of_token), _ptr(seq_slot), _ptr(q_start), T, n_seqs, proj.stride(0), int(off_conv),
+                                     int(off_b), heads, key_heads, d, dv, n_taps, float(eps), stage, _stream()))
+
+
 def attention_generic(q, q_stride: int, k_pool, v_pool, out, positions, seq_of_token, seq_slot, block_table,
                       status, nh: int, nkv: int, d: int, page_size: int, window: int, scale: float,
                       T: Optional[int] = None) -> None:
@@ -262,7 +436,7 @@ def gemm_plain(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, mode: int) -> 
         raise KernelError("gemm_plain: rows must be contiguous")
     M, K = a.shape
     N = c.shape[1]
-    rows = 2 * N if mode == GEMM_SWIGLU else N
+    rows = 2 * N if mode in GEMM_GATED else N
     if w.shape != (rows, K) or c.shape[0] != M:
         raise KernelError(f"gemm_plain: shapes a {tuple(a.shape)}, w {tuple(w.shape)}, c {tuple(c.shape)} do not fit")
     want = torch.float32 if mode in (GEMM_STORE_F32, GEMM_ACCUM_F32) else a.dtype

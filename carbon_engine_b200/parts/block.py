@@ -10,22 +10,32 @@ from .base import Block, BundleCacheSpec, FeedForward, Mixer, Norm, Part
 
 
 class PreNormBlock(Block):
-    def __init__(self, mixer_norm: Norm, mixer: Mixer, ffn_norm: Norm, ffn: FeedForward):
-        self.mixer_norm, self.mixer, self.ffn_norm, self.ffn = mixer_norm, mixer, ffn_norm, ffn
+    def __init__(self, mixer_norm: Norm, mixer: Mixer, ffn_norm: Optional[Norm] = None, ffn: Optional[FeedForward] = None,
+                 after: Optional[Part] = None):
+        """``ffn`` None: the layer has only the mixer.  ``after``: a part with ``forward(ctx, x)`` that adds into the
+        residual once the sublayers are done (a per-layer token input, for instance)."""
+        if (ffn is None) != (ffn_norm is None):
+            raise ValueError("a feed-forward and its norm come together")
+        self.mixer_norm, self.mixer, self.ffn_norm, self.ffn, self.after = mixer_norm, mixer, ffn_norm, ffn, after
 
     def children(self) -> List[Part]:
-        return [self.mixer_norm, self.mixer, self.ffn_norm, self.ffn]
+        return [p for p in (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn, self.after) if p is not None]
 
     def step_bytes(self, tokens: int, element_size: int) -> int:
         h = tokens * self.mixer_norm.width * element_size if hasattr(self.mixer_norm, "width") else 0
-        return h + max(self.mixer.step_bytes(tokens, element_size), self.ffn.step_bytes(tokens, element_size))
+        parts = [self.mixer.step_bytes(tokens, element_size)]
+        parts += [p.step_bytes(tokens, element_size) for p in (self.ffn, self.after) if p is not None]
+        return h + max(parts)
 
     def forward(self, ctx, x: torch.Tensor, cache) -> None:
         h = ctx.buffer(tuple(x.shape))
         self.mixer_norm.forward(x, h)
         self.mixer.forward(ctx, h, x, cache)
-        self.ffn_norm.forward(x, h)
-        self.ffn.forward(ctx, h, x)
+        if self.ffn is not None:
+            self.ffn_norm.forward(x, h)
+            self.ffn.forward(ctx, h, x)
+        if self.after is not None:
+            self.after.forward(ctx, x)
 
 
 class StreamBlock(Block):

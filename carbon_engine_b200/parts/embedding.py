@@ -17,8 +17,9 @@ from .linear import STORE_F32, matmul_nt
 
 
 class Embedding(Part):
-    def __init__(self, vocab: int, width: int, name: str):
-        self.vocab, self.width, self.name = vocab, width, name
+    def __init__(self, vocab: int, width: int, name: str, scale: float = 1.0):
+        """``scale`` multiplies every embedding row on its way into the residual stream."""
+        self.vocab, self.width, self.name, self.scale = vocab, width, name, float(scale)
         self.weight: Optional[torch.Tensor] = None
 
     def tensor_specs(self) -> List[TensorSpec]:
@@ -28,20 +29,21 @@ class Embedding(Part):
         self.weight = to_device(get(self.name), device, dtype)
 
     def forward(self, ctx, x: torch.Tensor) -> None:
-        ops.embed(self.weight, ctx.tokens, x, ctx.status)
+        ops.embed(self.weight, ctx.tokens, x, ctx.status, self.scale)
 
 
 class LMHead(Part):
     """Final norm + head product for chosen rows.  ``tied_to`` shares an embedding's tensor."""
 
     def __init__(self, vocab: int, width: int, norm: Norm, name: Optional[str], tied_to: Optional[Embedding] = None,
-                 redundant_name: Optional[str] = None):
-        """``redundant_name``: with a tied head, the name under which a checkpoint may still store a copy
+                 redundant_name: Optional[str] = None, logit_cap: float = 0.0):
+        """``logit_cap`` > 0: the logits become cap * tanh(logits / cap).  ``redundant_name``: with a tied head, the name under which a checkpoint may still store a copy
         of the head; it is ignored, as the reference ignores it (src/model/mod.rs:725)."""
         if (name is None) == (tied_to is None):
             raise ValueError("the head has either a tensor of its own or an embedding it is tied to")
         self.vocab, self.width, self.norm, self.name, self.tied_to = vocab, width, norm, name, tied_to
         self.redundant_name = redundant_name if tied_to is not None else None
+        self.logit_cap = float(logit_cap)
         self._weight: Optional[torch.Tensor] = None
 
     def ignorable_tensors(self) -> List[str]:
@@ -69,4 +71,6 @@ class LMHead(Part):
         z = ctx.buffer((R, self.width))
         self.norm.forward(x, z, rows)
         matmul_nt(z, self.weight, logits, STORE_F32)
+        if self.logit_cap > 0.0:
+            ops.tanh_cap(logits, self.logit_cap)
         return logits

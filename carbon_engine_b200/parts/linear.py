@@ -3,7 +3,8 @@
 A :class:`Linear` may be the row-wise concatenation of several stored tensors that share their
 input (q|k|v, gate|up), so that one product serves them all; the reference keeps them as separate
 products (src/model/attention.rs:871).  The epilogue is part of the product: store in the
-activation dtype, store float32 (logits), add into the float32 residual stream, or SwiGLU.
+activation dtype, store float32 (logits), add into the float32 residual stream, or a gated activation
+(SiLU or ReLU of the gate rows times the up rows).
 
 float32 runs the plain FMA kernel only.  bfloat16 runs the tensor-core kernels of
 ``csrc/kernels`` when they accept the shape and otherwise a library product (cuBLAS through
@@ -18,7 +19,7 @@ import torch
 from .. import ops
 from .base import Part, TensorGetter, TensorSpec, to_device
 
-STORE, STORE_F32, ACCUM, SWIGLU = ops.GEMM_STORE, ops.GEMM_STORE_F32, ops.GEMM_ACCUM_F32, ops.GEMM_SWIGLU
+STORE, STORE_F32, ACCUM, SWIGLU, RELUGLU = ops.GEMM_STORE, ops.GEMM_STORE_F32, ops.GEMM_ACCUM_F32, ops.GEMM_SWIGLU, ops.GEMM_RELUGLU
 
 #: bfloat16 products go to "tensor" (own tcgen05 kernels), "library" (cuBLAS + epilogue kernel) or
 #: "plain" (the FMA kernel); "auto" takes the first that accepts the shape.
@@ -58,6 +59,8 @@ def matmul_nt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, sc
         ops.add_residual(out, torch.matmul(a, w.t()))
     elif mode == SWIGLU:
         ops.swiglu(torch.matmul(a, w.t()), out)
+    elif mode == RELUGLU:
+        ops.reluglu(torch.matmul(a, w.t()), out)
     else:
         raise ValueError(f"unknown epilogue {mode}")
 
@@ -113,6 +116,6 @@ class Linear(Part):
         """``add_bias=False``: the caller adds ``self.bias`` itself (in a kernel that touches the output anyway)."""
         matmul_nt(a, self.weight, out, mode)
         if add_bias and self.bias is not None and a.shape[0] > 0:
-            if mode == SWIGLU:
-                raise ValueError("a bias before the SwiGLU epilogue is not supported")
+            if mode in (SWIGLU, RELUGLU):
+                raise ValueError("a bias before a gated epilogue is not supported")
             ops.add_bias(out, self.bias)

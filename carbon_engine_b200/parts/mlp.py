@@ -1,6 +1,6 @@
 """Gated feed-forward: down(act(gate(h)) * up(h)), added into the residual stream
-(src/model/layers.rs:568, 625-648; src/model/mod.rs:649).  Only SiLU is built; the gate and up
-weights are held as one matrix so that one product with a SwiGLU epilogue serves both."""
+(src/model/layers.rs:568, 625-648; src/model/mod.rs:649).  The activation is SiLU or ReLU; the gate and up
+weights are held as one matrix so that one product with a gated epilogue serves both."""
 from __future__ import annotations
 
 from typing import List, Sequence
@@ -8,7 +8,9 @@ from typing import List, Sequence
 import torch
 
 from .base import FeedForward, Part
-from .linear import ACCUM, STORE_F32, SWIGLU, Linear
+from .linear import ACCUM, RELUGLU, STORE_F32, SWIGLU, Linear
+
+_EPILOGUES = {"silu": SWIGLU, "relu": RELUGLU}
 
 
 class GatedMLP(FeedForward):
@@ -17,8 +19,9 @@ class GatedMLP(FeedForward):
     def __init__(self, hidden: int, intermediate: int, prefix: str, activation: str = "silu",
                  names: Sequence[str] = ("gate_proj.weight", "up_proj.weight", "down_proj.weight")):
         """``names``: the gate, up and down tensors' names under ``prefix``."""
-        if activation != "silu":
-            raise ValueError(f"activation '{activation}' is not supported (silu only)")
+        if activation not in _EPILOGUES:
+            raise ValueError(f"activation '{activation}' is not supported ({', '.join(sorted(_EPILOGUES))})")
+        self.epilogue = _EPILOGUES[activation]
         self.hidden, self.intermediate, self.prefix = hidden, intermediate, prefix
         gate, up, down = names
         self.gate_up = Linear(hidden, [intermediate, intermediate], [f"{prefix}.{gate}", f"{prefix}.{up}"])
@@ -32,5 +35,5 @@ class GatedMLP(FeedForward):
 
     def forward(self, ctx, h: torch.Tensor, x: torch.Tensor, accumulate: bool = True) -> None:
         act = ctx.buffer((h.shape[0], self.intermediate))
-        self.gate_up.forward(h, act, SWIGLU)
+        self.gate_up.forward(h, act, self.epilogue)
         self.down.forward(act, x, ACCUM if accumulate else STORE_F32)

@@ -28,13 +28,15 @@ def plain_schedule(n_blocks: int) -> List[LayerCall]:
 
 class DecoderModel(Part):
     def __init__(self, config, embedding: Embedding, blocks: Sequence[Block], head: LMHead,
-                 schedule: Optional[Sequence[LayerCall]] = None, streams: int = 0):
-        """``streams`` > 0: the residual is kept as that many copies [T, streams, width], all equal to the
+                 schedule: Optional[Sequence[LayerCall]] = None, streams: int = 0, extras: Sequence[Part] = ()):
+        """``extras``: parts with tensors of their own that several blocks refer to (a table that every layer reads a
+        slice of): loaded once, with the model.  ``streams`` > 0: the residual is kept as that many copies [T, streams, width], all equal to the
         embedding at the start; the blocks read and write them, the head's norm reads their sum."""
         self.config = config
         self.streams = int(streams)
         self.embedding = embedding
         self.blocks = list(blocks)
+        self.extras = list(extras)
         self.head = head
         self.schedule = list(schedule) if schedule is not None else plain_schedule(len(self.blocks))
         self.dtype: Optional[torch.dtype] = None
@@ -53,7 +55,7 @@ class DecoderModel(Part):
         self._writers = writers
 
     def children(self) -> List[Part]:
-        return [self.embedding, *self.blocks, self.head]
+        return [self.embedding, *self.extras, *self.blocks, self.head]
 
     @property
     def graph_safe(self) -> bool:

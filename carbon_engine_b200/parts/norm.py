@@ -49,3 +49,23 @@ class GroupedRMSNorm(Norm):
     def forward(self, x: torch.Tensor, out: torch.Tensor, rows: Optional[torch.Tensor] = None,
                 coef: Optional[torch.Tensor] = None) -> None:
         ops.streams_norm(x, self.weight, out, self.eps, self.groups, coef, rows)
+
+
+class LayerNorm(Norm):
+    """y = (x - mean) / sqrt(var + eps) * weight + bias, var the mean of the squared deviations; weight and bias in float32."""
+
+    def __init__(self, width: int, eps: float, name: str, bias_name: Optional[str] = None):
+        self.width, self.eps, self.name = int(width), float(eps), name
+        self.bias_name = bias_name or f"{name}.b"
+        self.weight: Optional[torch.Tensor] = None
+        self.bias: Optional[torch.Tensor] = None
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        return [TensorSpec(self.name, (self.width,), "norm"), TensorSpec(self.bias_name, (self.width,), "bias")]
+
+    def load(self, get: TensorGetter, device, dtype) -> None:
+        self.weight = get(self.name).to(device).to(torch.float32).contiguous()
+        self.bias = get(self.bias_name).to(device).to(torch.float32).contiguous()
+
+    def forward(self, x: torch.Tensor, out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
+        ops.layernorm(x, self.weight, self.bias, out, self.eps, rows)

@@ -10,8 +10,11 @@ from typing import Callable, Dict
 from .attention import PagedAttention
 from .delta_rule import GeneralDeltaRule
 from .diff_attention import DifferentialAttention
+from .gated_delta import ChannelGatedDelta
+from .latent_attention import LatentAttention
+from .masked_attention import GatedWindowAttention
 from .mlp import GatedMLP
-from .norm import GroupedRMSNorm, RMSNorm
+from .norm import GroupedRMSNorm, LayerNorm, RMSNorm
 from .rope import NoPositionEncoding, RotaryEmbedding
 
 _KINDS: Dict[str, Dict[str, Callable]] = {"mixer": {}, "feed_forward": {}, "norm": {}, "position": {}}
@@ -46,8 +49,12 @@ register_mixer("full_attention", lambda **kw: PagedAttention(**{**kw, "window": 
 register_mixer("sliding_attention", lambda **kw: PagedAttention(**kw))
 register_mixer("differential_attention", DifferentialAttention)
 register_mixer("general_delta", GeneralDeltaRule)
+register_mixer("gated_window_attention", GatedWindowAttention)
+register_mixer("latent_attention", LatentAttention)
+register_mixer("channel_gated_delta", ChannelGatedDelta)
 register_feed_forward("gated_mlp", GatedMLP)
 register_norm("rmsnorm", RMSNorm)
 register_norm("grouped_rmsnorm", GroupedRMSNorm)
+register_norm("layernorm", LayerNorm)
 register_position("rotary", RotaryEmbedding)
 register_position("none", lambda **kw: NoPositionEncoding())
