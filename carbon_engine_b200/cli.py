@@ -112,13 +112,21 @@ def cmd_tiny_model(a) -> int:
     from . import models  # noqa: F401
     from .config.qwen3 import Qwen3Config
     from .weights.loader import write_random_model
-    if a.arch not in ("qwen3", "munizen"):
-        raise SystemExit(f"--arch {a.arch}: qwen3 and munizen are built")
+    if a.arch not in ("qwen3", "munizen", "lunerax"):
+        raise SystemExit(f"--arch {a.arch}: qwen3, munizen and lunerax are built")
     heads = a.heads or 4
     head_dim = a.head_dim or 16
     store = {"f32": torch.float32, "bf16": torch.bfloat16}.get(a.dtype)
     if store is None:
         raise SystemExit("--dtype must be f32 or bf16")
+    if a.arch == "lunerax":
+        # layers go attention (capped scores, a window that keeps first tokens), delta rule, delta rule, latent attention
+        from .config.lunerax import sketch_config
+        cfg = sketch_config(a.vocab, a.hidden, a.layers, heads, a.kv_heads or max(1, heads // 2), head_dim,
+                            a.intermediate or 2 * a.hidden, window=a.mask_size, side_dim=a.side_dim, max_positions=a.max_positions,
+                            eps=a.rms_norm_eps, rope_base=a.rope_theta)
+        print(f"wrote {write_random_model(cfg, a.out, seed=a.seed, store_dtype=store)}")
+        return 0
     if a.arch == "munizen":
         # layers alternate between the recurrent mixer (no feed-forward) and differential attention (with one);
         # a map of a head is half of --head-dim, a value head is --head-dim
@@ -180,9 +188,10 @@ def main(argv: Optional[List[str]] = None) -> int:
 
     t = sub.add_parser("tiny-model", help="write a small random model folder")
     t.add_argument("--out", required=True)
-    t.add_argument("--arch", default="qwen3", help="qwen3 | munizen")
+    t.add_argument("--arch", default="qwen3", help="qwen3 | munizen | lunerax")
+    t.add_argument("--side-dim", type=int, default=8, help="lunerax: width of the per-layer token input (0: none)")
     t.add_argument("--streams", type=int, default=2, help="munizen: residual streams (0: an ordinary residual)")
-    t.add_argument("--mask-size", type=int, default=256, help="munizen: positions in a block of the attention mask")
+    t.add_argument("--mask-size", type=int, default=256, help="munizen: positions in a block of the attention mask; lunerax: the sliding window")
     t.add_argument("--layers", type=int, default=4)
     t.add_argument("--hidden", type=int, default=64)
     t.add_argument("--heads", type=int, default=None)

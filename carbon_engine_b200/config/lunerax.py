@@ -162,3 +162,34 @@ class LuneraxConfig(ModelConfig):
         if self.eos_token_ids:
             out["eos_token_id"] = list(self.eos_token_ids) if len(self.eos_token_ids) > 1 else self.eos_token_ids[0]
         return out
+
+
+def sketch_config(vocab: int, width: int, n_layers: int, heads: int, kv_heads: int, head_dim: int, ff: int, window: int = 1024,
+                  keep_first: int = 4, side_dim: int = 0, max_positions: int = DEFAULT_MAX_POSITIONS, eps: float = 1e-6,
+                  rope_base: float = 10000.0, softcap: float = 30.0, logit_softcap: float = 30.0) -> LuneraxConfig:
+    """A configuration of the usual proportions from a few sizes, for random-weight models (the command line's
+    ``tiny-model``, measurements): layers go attention, delta rule, delta rule, latent attention and again; attention heads of
+    ``head_dim`` for keys and values alike with blended values; delta heads of ``head_dim`` filling the width; latents of a
+    quarter of the width (keys/values) and half of it (queries) with a rotated part of half a head."""
+    delta_heads = max(1, width // head_dim)
+    rot = max(2, head_dim // 4 * 2)
+    kinds = (ATTENTION, CHANNEL_DELTA, CHANNEL_DELTA, LATENT_ATTENTION)
+    layers = []
+    for i in range(n_layers):
+        kind = kinds[i % 4]
+        if kind == ATTENTION:
+            m = {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "scale": head_dim ** -0.5,
+                 "softcap": softcap, "mask": {"size": window, "keep_first": keep_first}, "v_mix": True}
+        elif kind == CHANNEL_DELTA:
+            m = {"heads": delta_heads, "kv_heads": delta_heads, "dim": head_dim, "vdim": head_dim, "conv": 4,
+                 "a_rank": max(8, width // 32 * 2), "g_rank": max(8, width // 32 * 2)}
+        else:
+            m = {"heads": heads, "dim": head_dim, "rot_dim": rot, "vdim": head_dim, "q_rank": max(8, width // 16 * 8),
+                 "kv_rank": max(8, width // 32 * 8), "scale": (head_dim + rot) ** -0.5, "rot": {"dims": rot, "base": rope_base},
+                 "mask": {"size": window}}
+        layers.append({"type": kind, "mixer": m, "mlp": {"kind": "dense", "ff": ff}})
+    raw = {"architecture": "Lunerax", "vocab": vocab, "width": width, "layers": layers, "norm": {"eps": eps},
+           "embedding": {"scale": float(width) ** 0.5}, "logit_softcap": logit_softcap, "max_position_embeddings": max_positions}
+    if side_dim > 0:
+        raw["token_side"] = {"dim": side_dim}
+    return LuneraxConfig.from_dict(raw)

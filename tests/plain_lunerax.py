@@ -195,3 +195,25 @@ def forward(cfg: dict, weights: Dict[str, torch.Tensor], tokens: List[int], laye
     z = layer_norm(x, w["final.norm"], w["final.norm.b"], eps) @ w["head"].T
     cap = float(cfg.get("logit_softcap") or 0.0)
     return cap * torch.tanh(z / cap) if cap > 0.0 else z
+
+
+def read_model(folder: str):
+    """(config dict, weights dict) of a model folder: config.json and model.safetensors (an 8-byte little-endian header
+    length, a JSON header name -> dtype, shape, data_offsets, then the data)."""
+    import json
+    import os
+    import struct
+    with open(os.path.join(folder, "config.json")) as fh:
+        cfg = json.load(fh)
+    with open(os.path.join(folder, "model.safetensors"), "rb") as fh:
+        blob = fh.read()
+    (n,) = struct.unpack("<Q", blob[:8])
+    header = json.loads(blob[8:8 + n].decode())
+    weights = {}
+    for name, meta in header.items():
+        if name == "__metadata__":
+            continue
+        lo, hi = meta["data_offsets"]
+        dt = {"F32": torch.float32, "BF16": torch.bfloat16, "I32": torch.int32}[meta["dtype"]]
+        weights[name] = torch.frombuffer(bytearray(blob[8 + n + lo:8 + n + hi]), dtype=dt).reshape(meta["shape"]).clone()
+    return cfg, weights
