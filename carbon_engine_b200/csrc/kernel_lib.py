@@ -55,6 +55,11 @@ _SIGNATURES = {
     # q, k_pool, v_pool, gate, out, dtype, positions, seq_of_token, seq_slot, block_table, status, T, nh, nkv, d, dv,
     # q_stride, q_head, ldk, ldv, gate_stride, page_size, max_pages, num_pages, window, keep_first, scale, softcap, stream
     "ce_masked_attention": (_i, [_p] * 5 + [_i] + [_p] * 5 + [_i] * 15 + [_f, _f, _p]),
+    # d, dv, q_stride, q_head, ldk, ldv, alias
+    "ce_masked_attention_mma_supported": (_i, [_i] * 7),
+    # q, k_pool, v_pool, gate, out, positions, seq_slot, q_start, block_table, tiles, status, n_tiles, n_tokens, nh, nkv, d, dv,
+    # q_stride, q_head, ldk, ldv, gate_stride, page_size, max_pages, num_pages, window, keep_first, scale, softcap, stream
+    "ce_masked_attention_mma": (_i, [_p] * 11 + [_i] * 16 + [_f, _f, _p]),
     "ce_gated_delta_prep_width": (_i, [_i, _i, _i, _i]),
     # proj, dec, gz, taps, a_log, dt_bias, norm_w, prep, raw, state, kept, out, out_dtype, seq_of_token, seq_slot, q_start,
     # T, B, ld, off_conv, off_b, H, G, d, dv, K, eps, stage, stream

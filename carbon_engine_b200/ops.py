@@ -376,8 +376,23 @@ def masked_attention(q, q_head: int, k_pool, v_pool, ldk: int, ldv: int, gate, o
         float(scale), float(softcap), _stream()))
 
 
-def masked_attention_mma_supported(d: int, dv: int, q_stride: int, q_head: int, ldk: int, ldv: int) -> bool:
-    return False
+def masked_attention_mma_supported(d: int, dv: int, q_stride: int, q_head: int, ldk: int, ldv: int, alias: bool) -> bool:
+    return bool(kernels().ce_masked_attention_mma_supported(d, dv, q_stride, q_head, ldk, ldv, 1 if alias else 0))
+
+
+def masked_attention_mma(q, q_head: int, k_pool, v_pool, ldk: int, ldv: int, gate, out, positions, seq_slot, q_start, block_table,
+                         tiles, n_tiles: int, status, nh: int, nkv: int, d: int, dv: int, page_size: int, window: int,
+                         keep_first: int, scale: float, softcap: float) -> None:
+    """:func:`masked_attention` on the tensor cores (bfloat16) for tiles of 64 query tokens: ``tiles`` holds (sequence, first
+    token within the sequence's tokens of the step) pairs.  ``gate`` holds bfloat16 logits."""
+    _need(k_pool, "k_pool", torch.bfloat16); _need(out, "out", torch.bfloat16)
+    if q.dtype != torch.bfloat16 or v_pool.dtype != torch.bfloat16 or (gate is not None and gate.dtype != torch.bfloat16):
+        raise KernelError("masked_attention_mma: bfloat16 only")
+    _ok(kernels().ce_masked_attention_mma(
+        _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(gate), _ptr(out), _ptr(positions), _ptr(seq_slot), _ptr(q_start), _ptr(block_table),
+        _ptr(tiles), _ptr(status), int(n_tiles), out.shape[0], nh, nkv, d, dv, q.stride(0), int(q_head), int(ldk), int(ldv),
+        gate.stride(0) if gate is not None else 0, page_size, block_table.shape[1], k_pool.shape[0], int(window), int(keep_first),
+        float(scale), float(softcap), _stream()))
 
 
 def gated_delta_prep_width(heads: int, key_heads: int, d: int, dv: int) -> int:

@@ -55,7 +55,7 @@ def attend(ctx, plan, q, q_head, cache, ldk, ldv, v_pool, gate, out, table, nh, 
         prof.note_work((keys * nkv * (d + (dv if v_pool is not cache.k_pool else 0)) + ctx.T * nh * (d + dv)) * el,
                        2 * pairs * nh * (d + dv))
     if q.dtype == torch.bfloat16 and ctx.fast_attention and plan is not None and \
-            ops.masked_attention_mma_supported(d, dv, q.stride(0), q_head, ldk, ldv):
+            ops.masked_attention_mma_supported(d, dv, q.stride(0), q_head, ldk, ldv, v_pool is cache.k_pool):
         ops.masked_attention_mma(q, q_head, cache.k_pool, v_pool, ldk, ldv, gate, out, ctx.positions, ctx.seq_slot, ctx.q_start,
                                  table, plan.tiles, plan.n_tiles, ctx.status, nh, nkv, d, dv, cache.page_size, window, keep_first,
                                  scale, softcap)
