@@ -168,10 +168,37 @@ def munizen_config(width, heads, kv_heads, ff, layers, vocab):
                                     "norm": {"eps": 1e-6, "groups": 2}, "streams": 2, "max_position_embeddings": 8192})
 
 
+def lunerax_config(width, heads, kv_heads, ff, layers, vocab):
+    """A Lunerax model of the usual proportions at the Qwen3 model's layer sizes: layers go attention (heads of 128, capped
+    scores, a window of 1,024 that keeps 4 first tokens, blended values), delta rule, delta rule (state heads of 128 x 128,
+    4 taps), latent attention (a cached row of 256 + 32 per token, a window of 1,024); every layer with the feed-forward
+    and a per-layer token input of 128."""
+    from carbon_engine_b200.config.lunerax import LuneraxConfig
+    ffn = {"kind": "dense", "ff": ff}
+    attn = {"type": "attention", "mlp": ffn,
+            "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "softcap": 30.0,
+                      "mask": {"size": 1024, "keep_first": 4}, "v_mix": True}}
+    delta = {"type": "channel_delta", "mlp": ffn,
+             "mixer": {"heads": width // 128, "kv_heads": width // 128, "dim": 128, "vdim": 128, "conv": 4, "a_rank": 64, "g_rank": 64}}
+    latent = {"type": "latent_attention", "mlp": ffn,
+              "mixer": {"heads": heads, "dim": 128, "rot_dim": 32, "vdim": 128, "q_rank": width // 4, "kv_rank": 256,
+                        "scale": 160 ** -0.5, "rot": {"dims": 32, "base": 1e6}, "mask": {"size": 1024}}}
+    kinds = (attn, delta, delta, latent)
+    return LuneraxConfig.from_dict({"architecture": "Lunerax", "vocab": vocab, "width": width,
+                                    "layers": [kinds[i % 4] for i in range(layers)], "norm": {"eps": 1e-6},
+                                    "embedding": {"scale": float(width) ** 0.5}, "logit_softcap": 30.0,
+                                    "token_side": {"dim": 128}, "max_position_embeddings": 8192})
+
+
 def compare_designs(args, BenchHarness, pk) -> int:
-    """Prefill and decode throughput of the Munizen design beside the Qwen3 dense design at equal layer sizes
-    (random weights, a few layers), with the kernels of each and their distance from the roofline."""
+    """Prefill and decode throughput of the engine's other designs (--designs: munizen, lunerax) beside the Qwen3 dense
+    design at equal layer sizes (random weights, a few layers), with the kernels of each and their distance from the roofline."""
     import torch
+    makers = {"munizen": munizen_config, "lunerax": lunerax_config}
+    designs = [x for x in args.designs.split(",") if x != "qwen3"]
+    for x in designs:
+        if x not in makers:
+            raise SystemExit(f"--designs {x}: munizen, lunerax and qwen3 are built")
     layers = args.layers if args.layers != SIZES_8B["num_hidden_layers"] else 4
     vocab, out = 32768, {}
     for name in args.sizes.split(","):
@@ -179,7 +206,7 @@ def compare_designs(args, BenchHarness, pk) -> int:
         qwen = dict(SIZES_8B, num_hidden_layers=layers, hidden_size=width, num_attention_heads=heads,
                     num_key_value_heads=kv_heads, head_dim=128, intermediate_size=ff, vocab_size=vocab, max_position_embeddings=8192)
         row = {}
-        for design, cfg in (("munizen", munizen_config(width, heads, kv_heads, ff, layers, vocab)), ("qwen3", qwen)):
+        for design, cfg in [(x, makers[x](width, heads, kv_heads, ff, layers, vocab)) for x in designs] + [("qwen3", qwen)]:
             h = BenchHarness(cfg, max_batch=max(args.batch, 2), context=args.context, new_tokens=256, graphs=not args.no_graphs,
                              step_tokens=max(4096, args.prefill_tokens))
             pf = h.prefill(args.prefill_tokens, 3, 2)
@@ -229,6 +256,8 @@ def main() -> int:
     ap.add_argument("--no-check", action="store_true", help="skip the comparison of a short greedy continuation with float32")
     ap.add_argument("--sizes", default="1b,8b", help="with --workload compare-designs: which of the layer sizes "
                     "1b, 4b, 8b (width / heads / feed-forward of models of about that size), with commas between them")
+    ap.add_argument("--designs", default="munizen,qwen3", help="with --workload compare-designs: the designs set beside one another "
+                    "(munizen, lunerax; qwen3 is always the last)")
     ap.add_argument("--workload", default="decode", choices=["decode", "mixed-14b", "batch16-32b", "compare-designs"],
                     help="decode: the contract's line (default).  mixed-14b: 32 requests with prompts of 128 to 3,072 tokens at "
                          "Qwen3-14B sizes, prompts cut under a 2,048-token step budget beside the decoding requests, 128 new "
