@@ -15,11 +15,16 @@
 //
 // K and V tiles come from the pages by cp.async into two buffers, a tile ahead of the arithmetic; the page of every key
 // row of a tile is looked up two tiles ahead.  Key tiles that no row of the block can see (between the kept first tokens
-// and the window) are passed over.
+// and the window) are passed over.  A key tile has 64 keys, or 32 where wide key rows would otherwise leave room for one
+// block an SM only.
+//
+// A block of at most 16 rows (a step of single tokens) is work for one warp, whose instructions one after another are what
+// the block's time is made of.  Where the launch has no more blocks than the GPU has SMs, the kernel gets four buffers and
+// the four warps take four tiles of keys side by side, each with a running maximum and sum of its own; their partial rows
+// are merged through shared memory in the order of the warps.
 #include "common.cuh"
 
 #define MM_BM 64
-#define MM_BN 64
 #define MM_SUB 32                // keys of a tile whose scores a warp holds at a time
 #define MM_THREADS 128
 #define MM_PAD 8                 // bf16 elements of padding per shared-memory row (16 bytes: conflict-free ldmatrix)
@@ -39,6 +44,7 @@ struct MaskedMmaArgs {
     int nh, nkv, d, dv, q_stride, q_head, ldk, ldv, gate_stride, page_size, max_pages, num_pages, window, keep_first;
     int pack;                    // heads of one key head a block takes (a power of two up to 16 that divides nh / nkv)
     int slice;                   // value columns a block takes (a multiple of 16)
+    int share;                   // 1: four K/V buffers are there, and blocks of at most 16 rows spread their key tiles over the warps
     float scale, softcap;
 };
 
@@ -54,14 +60,20 @@ __device__ __forceinline__ void mm_mma(float* c, const unsigned* a, unsigned b0,
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// tanh in one MUFU instruction (absolute error about 5e-4): the capped score is rounded far more coarsely by its bfloat16 operands
+__device__ __forceinline__ float mm_tanh_fast(float x) {
+    float y;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ unsigned mm_pack(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<unsigned*>(&v);
 }
 
 // DVT: 8-column tiles of a value slice the registers hold (slice <= 8 DVT); ALIAS: the values are the key rows' leading part
-template <int DVT, bool ALIAS>
-__global__ void __launch_bounds__(MM_THREADS, (DVT <= 16 ? 3 : 1)) masked_attention_mma_kernel(MaskedMmaArgs a) {
+template <int DVT, bool ALIAS, int MM_BN>
+__global__ void __launch_bounds__(MM_THREADS, 3) masked_attention_mma_kernel(MaskedMmaArgs a) {
     ce_pdl_begin();
     extern __shared__ __align__(16) unsigned char mm_smem[];
     const int d = a.d, ldq = d + MM_PAD, ldks = d + MM_PAD;
@@ -81,7 +93,7 @@ __global__ void __launch_bounds__(MM_THREADS, (DVT <= 16 ? 3 : 1)) masked_attent
     __nv_bfloat16* stage0 = Qs + MM_BM * ldq;                // two buffers of K [64][ldks] (and V [64][ldvs])
     const int stage_elems = MM_BN * ldks + (ALIAS ? 0 : MM_BN * ldvs);
     __shared__ int s_pos[MM_BM];
-    __shared__ int s_page[2][MM_BN];                         // page of every key row of the tile a buffer will hold
+    __shared__ int s_page[4][MM_BN];                         // page of every key row of the tile a buffer will hold
 
     const int* table = a.block_table + (size_t)a.seq_slot[b] * a.max_pages;
     if (tid < MM_BM) s_pos[tid] = tid < n_rows ? a.positions[t0 + tid / pack] : -1;
@@ -96,8 +108,10 @@ __global__ void __launch_bounds__(MM_THREADS, (DVT <= 16 ? 3 : 1)) masked_attent
     const int pos_first = s_pos[0], pos_last = s_pos[n_rows - 1];
     const int keep = a.window > 0 ? a.keep_first : 0;
     const int lo_blk = a.window > 0 ? max(0, pos_first - a.window + 1) : 0;
+    // few rows: the warps all take rows 0..15 and share the key tiles; else warp w takes rows 16 w ..
+    const bool share_keys = a.share != 0 && n_rows <= 16 && pos_last - lo_blk / MM_BN * MM_BN >= MM_BN;
     // this thread's two rows
-    const int row0 = warp * 16;
+    const int row0 = share_keys ? 0 : warp * 16;
     const int ra = row0 + (lane >> 2), rb = ra + 8;
     const int pos_a = s_pos[ra], pos_b = s_pos[rb];
     const int lo_a = a.window > 0 ? max(0, pos_a - a.window + 1) : 0, lo_b = a.window > 0 ? max(0, pos_b - a.window + 1) : 0;
@@ -121,33 +135,31 @@ __global__ void __launch_bounds__(MM_THREADS, (DVT <= 16 ? 3 : 1)) masked_attent
     auto stage = [&](int k0, int which) {
         __nv_bfloat16* Kd = stage0 + which * stage_elems;
         const int* pages = s_page[which];
-        {   // K: two threads a row, each every second 16-byte piece
-            int r = tid >> 1;
+        constexpr int TPR = MM_THREADS / MM_BN;           // threads a key row: each takes every TPR-th 16-byte piece
+        const int r = tid / TPR, c_first = (tid % TPR) * 8;
+        const int page = pages[r];
+        {
             __nv_bfloat16* dst = Kd + r * ldks;
-            int page = pages[r];
             if (page >= 0) {
                 const __nv_bfloat16* src = a.k_pool + (((size_t)page * a.nkv + kvh) * a.page_size + (k0 + r) % a.page_size) * a.ldk;
-                for (int c = (tid & 1) * 8; c < d; c += 16) {
+                for (int c = c_first; c < d; c += TPR * 8) {
                     unsigned sa = (unsigned)__cvta_generic_to_shared(dst + c);
                     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sa), "l"(src + c));
                 }
             } else {
-                for (int c = (tid & 1) * 8; c < d; c += 16) *reinterpret_cast<uint4*>(dst + c) = make_uint4(0u, 0u, 0u, 0u);
+                for (int c = c_first; c < d; c += TPR * 8) *reinterpret_cast<uint4*>(dst + c) = make_uint4(0u, 0u, 0u, 0u);
             }
         }
-        if (!ALIAS) {   // V: two threads a row
-            __nv_bfloat16* Vd = Kd + MM_BN * ldks;
-            int r = tid >> 1;
-            __nv_bfloat16* dst = Vd + r * ldvs;
-            int page = pages[r];
+        if (!ALIAS) {
+            __nv_bfloat16* dst = Kd + MM_BN * ldks + r * ldvs;
             if (page >= 0) {
                 const __nv_bfloat16* src = a.v_pool + (((size_t)page * a.nkv + kvh) * a.page_size + (k0 + r) % a.page_size) * a.ldv + col0;
-                for (int c = (tid & 1) * 8; c < ncol; c += 16) {
+                for (int c = c_first; c < ncol; c += TPR * 8) {
                     unsigned sa = (unsigned)__cvta_generic_to_shared(dst + c);
                     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sa), "l"(src + c));
                 }
             } else {
-                for (int c = (tid & 1) * 8; c < ncol; c += 16) *reinterpret_cast<uint4*>(dst + c) = make_uint4(0u, 0u, 0u, 0u);
+                for (int c = c_first; c < ncol; c += TPR * 8) *reinterpret_cast<uint4*>(dst + c) = make_uint4(0u, 0u, 0u, 0u);
             }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
@@ -195,7 +207,7 @@ __global__ void __launch_bounds__(MM_THREADS, (DVT <= 16 ? 3 : 1)) masked_attent
                         int key = ks0 + nt * 8 + (lane & 3) * 2 + (e & 1);
                         see = upper ? (key <= pos_a && (key >= lo_a || key < keep)) : (key <= pos_b && (key >= lo_b || key < keep));
                     }
-                    float v = a.softcap > 0.f ? cap2 * tanhf(s[nt][e] * pre_cap) : s[nt][e] * scale2;
+                    float v = a.softcap > 0.f ? cap2 * mm_tanh_fast(s[nt][e] * pre_cap) : s[nt][e] * scale2;
                     v = see ? v : -INFINITY;
                     s[nt][e] = v;
                     if (upper) mx_a = fmaxf(mx_a, v); else mx_b = fmaxf(mx_b, v);
@@ -249,6 +261,68 @@ __global__ void __launch_bounds__(MM_THREADS, (DVT <= 16 ? 3 : 1)) masked_attent
     const int n_keep = min((keep + MM_BN - 1) / MM_BN, k_first / MM_BN);
     const int n_key_tiles = n_keep + (pos_last - k_first) / MM_BN + 1;
     auto k0_of = [&](int i) -> int { return i < n_key_tiles ? (i < n_keep ? i * MM_BN : k_first + (i - n_keep) * MM_BN) : -MM_BN; };
+    if (share_keys) {
+        // four tiles of keys at a time, one for each warp; the partial rows are merged afterwards
+        for (int g0 = 0; g0 < n_key_tiles; g0 += 4) {
+            if (tid < MM_BN)
+                for (int w = 0; w < 4; ++w) s_page[w][tid] = page_of(k0_of(g0 + w), tid);
+            __syncthreads();
+            for (int w = 0; w < 4; ++w)
+                if (g0 + w < n_key_tiles) stage(k0_of(g0 + w), w);
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+            __syncthreads();
+            if (g0 + warp < n_key_tiles) tile_math(k0_of(g0 + warp), warp);
+            __syncthreads();
+        }
+        // partial rows of warps 1..3: the sums so far [3][16][slice] and (maximum, sum) [3][16][2]; warp 0 adds them up in order
+        float* part = (float*)stage0;
+        float* ml = part + 3 * 16 * a.slice;
+        const int r_lo = lane >> 2, r_hi = r_lo + 8, cq2 = (lane & 3) * 2;
+        if (warp != 0) {
+            float* mine = part + (warp - 1) * 16 * a.slice;
+#pragma unroll
+            for (int nt = 0; nt < DVT; ++nt) {
+                if (nt * 8 < ncol) {
+                    *reinterpret_cast<float2*>(mine + r_lo * a.slice + nt * 8 + cq2) = make_float2(o[nt][0], o[nt][1]);
+                    *reinterpret_cast<float2*>(mine + r_hi * a.slice + nt * 8 + cq2) = make_float2(o[nt][2], o[nt][3]);
+                }
+            }
+            if ((lane & 3) == 0) {
+                float* m2 = ml + (warp - 1) * 16 * 2;
+                m2[r_lo * 2] = m_a; m2[r_lo * 2 + 1] = l_a;
+                m2[r_hi * 2] = m_b; m2[r_hi * 2 + 1] = l_b;
+            }
+        }
+        __syncthreads();
+        if (warp != 0) return;
+        float big_a = m_a, big_b = m_b;
+#pragma unroll
+        for (int w = 0; w < 3; ++w) {
+            big_a = fmaxf(big_a, ml[(w * 16 + r_lo) * 2]);
+            big_b = fmaxf(big_b, ml[(w * 16 + r_hi) * 2]);
+        }
+        float f_a = m_a == -INFINITY ? 0.f : ce_exp2_fast(m_a - big_a), f_b = m_b == -INFINITY ? 0.f : ce_exp2_fast(m_b - big_b);
+        l_a *= f_a; l_b *= f_b;
+#pragma unroll
+        for (int i = 0; i < DVT; ++i) { o[i][0] *= f_a; o[i][1] *= f_a; o[i][2] *= f_b; o[i][3] *= f_b; }
+#pragma unroll
+        for (int w = 0; w < 3; ++w) {
+            const float* theirs = part + w * 16 * a.slice;
+            float ma = ml[(w * 16 + r_lo) * 2], mb = ml[(w * 16 + r_hi) * 2];
+            float g_a = ma == -INFINITY ? 0.f : ce_exp2_fast(ma - big_a), g_b = mb == -INFINITY ? 0.f : ce_exp2_fast(mb - big_b);
+            l_a = fmaf(ml[(w * 16 + r_lo) * 2 + 1], g_a, l_a);
+            l_b = fmaf(ml[(w * 16 + r_hi) * 2 + 1], g_b, l_b);
+#pragma unroll
+            for (int nt = 0; nt < DVT; ++nt) {
+                if (nt * 8 < ncol) {
+                    float2 xa = *reinterpret_cast<const float2*>(theirs + r_lo * a.slice + nt * 8 + cq2);
+                    float2 xb = *reinterpret_cast<const float2*>(theirs + r_hi * a.slice + nt * 8 + cq2);
+                    o[nt][0] = fmaf(xa.x, g_a, o[nt][0]); o[nt][1] = fmaf(xa.y, g_a, o[nt][1]);
+                    o[nt][2] = fmaf(xb.x, g_b, o[nt][2]); o[nt][3] = fmaf(xb.y, g_b, o[nt][3]);
+                }
+            }
+        }
+    } else {
     if (tid < MM_BN) {
         s_page[0][tid] = page_of(k0_of(0), tid);
         s_page[1][tid] = page_of(k0_of(1), tid);
@@ -270,6 +344,7 @@ __global__ void __launch_bounds__(MM_THREADS, (DVT <= 16 ? 3 : 1)) masked_attent
         tile_math(k0_of(it), cur);
         if (tid < MM_BN) s_page[cur][tid] = page_ahead;      // buffer ``cur`` will hold the tile after the next
         __syncthreads();
+    }
     }
     const int cq = (lane & 3) * 2;
     float i_a = l_a > 0.f ? 1.0f / l_a : 0.f, i_b = l_b > 0.f ? 1.0f / l_b : 0.f;
@@ -301,26 +376,42 @@ __global__ void __launch_bounds__(MM_THREADS, (DVT <= 16 ? 3 : 1)) masked_attent
     }
 }
 
-static int mm_slice(int dv) { return dv <= 256 ? dv : 256; }
+static int mm_slice(int dv) { return dv <= 128 ? dv : 128; }
 
-static size_t mm_smem_bytes(int d, int dv, bool alias) {
-    size_t stage = (size_t)MM_BN * (d + MM_PAD) + (alias ? 0 : (size_t)MM_BN * (mm_slice(dv) + MM_PAD));
-    return ((size_t)MM_BM * (d + MM_PAD) + 2 * stage) * sizeof(__nv_bfloat16);
+// keys a tile: 64, or 32 where two buffers of 64 wide key rows would leave room for one block an SM only
+static int mm_key_tile(int d, int dv, bool alias) {
+    size_t stage64 = (size_t)64 * (d + MM_PAD) + (alias ? 0 : (size_t)64 * (mm_slice(dv) + MM_PAD));
+    return ((size_t)MM_BM * (d + MM_PAD) + 2 * stage64) * sizeof(__nv_bfloat16) > 100 * 1024 ? 32 : 64;
+}
+
+static size_t mm_smem_bytes(int d, int dv, bool alias, int buffers) {
+    int bn = mm_key_tile(d, dv, alias);
+    size_t stage = (size_t)bn * (d + MM_PAD) + (alias ? 0 : (size_t)bn * (mm_slice(dv) + MM_PAD));
+    size_t bytes = (size_t)buffers * stage * sizeof(__nv_bfloat16);
+    size_t merge = (size_t)(3 * 16 * mm_slice(dv) + 3 * 16 * 2) * sizeof(float);           // the partial rows of a shared walk
+    if (buffers == 4 && bytes < merge) bytes = merge;
+    return (size_t)MM_BM * (d + MM_PAD) * sizeof(__nv_bfloat16) + bytes;
 }
 
 // alias != 0: the value pool is the key pool (values = the key rows' leading dv elements)
 extern "C" int ce_masked_attention_mma_supported(int d, int dv, int q_stride, int q_head, int ldk, int ldv, int alias) {
     if (d < 16 || d % 16 || dv < 16 || dv % 16 || q_stride % 8 || q_head % 8 || ldk % 8 || ldv % 8) return 0;
     if (alias && dv > d) return 0;
-    return mm_smem_bytes(d, dv, alias != 0) <= 200 * 1024;
+    return mm_smem_bytes(d, dv, alias != 0, 2) <= 200 * 1024;
+}
+
+template <int DVT, bool ALIAS, int BN>
+static void mm_launch(const MaskedMmaArgs& a, dim3 grid, size_t smem, cudaStream_t stream) {
+    if (smem > 40 * 1024)            // the kernel's static arrays count toward the 48 KB a launch gets without asking
+        cudaFuncSetAttribute(masked_attention_mma_kernel<DVT, ALIAS, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    ce_note("masked_attention_mma_kernel");
+    ce_launch(masked_attention_mma_kernel<DVT, ALIAS, BN>, grid, MM_THREADS, smem, stream, a);
 }
 
 template <int DVT, bool ALIAS>
-static void mm_launch(const MaskedMmaArgs& a, dim3 grid, size_t smem, cudaStream_t stream) {
-    if (smem > 40 * 1024)            // the kernel's static arrays count toward the 48 KB a launch gets without asking
-        cudaFuncSetAttribute(masked_attention_mma_kernel<DVT, ALIAS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    ce_note("masked_attention_mma_kernel");
-    ce_launch(masked_attention_mma_kernel<DVT, ALIAS>, grid, MM_THREADS, smem, stream, a);
+static void mm_launch_bn(const MaskedMmaArgs& a, int bn, dim3 grid, size_t smem, cudaStream_t stream) {
+    if (bn == 32) mm_launch<DVT, ALIAS, 32>(a, grid, smem, stream);
+    else mm_launch<DVT, ALIAS, 64>(a, grid, smem, stream);
 }
 
 extern "C" int ce_masked_attention_mma(const void* q, const void* k_pool, const void* v_pool, const void* gate, void* out,
@@ -347,17 +438,21 @@ extern "C" int ce_masked_attention_mma(const void* q, const void* k_pool, const 
     int slice = mm_slice(dv);
     MaskedMmaArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, (const __nv_bfloat16*)gate,
                     (__nv_bfloat16*)out, positions, seq_slot, q_start, block_table, tiles, status, nh, nkv, d, dv, q_stride, q_head,
-                    ldk, ldv, gate_stride, page_size, max_pages, num_pages, window, keep_first, pack, slice, scale, softcap};
+                    ldk, ldv, gate_stride, page_size, max_pages, num_pages, window, keep_first, pack, slice, 0, scale, softcap};
     dim3 grid(n_tiles * pack, nh / pack, (dv + slice - 1) / slice);
-    size_t smem = mm_smem_bytes(d, dv, alias);
+    // Few blocks (a step of single tokens): four buffers, so that the warps can take four tiles of keys side by side.  Blocks
+    // of a packed tile that hold no token leave at once, so what counts is the tiles, not the grid.
+    int buffers = 2;
+    if ((long long)n_tiles * grid.y * grid.z <= (long long)ce_sm_count() && mm_smem_bytes(d, dv, alias, 4) <= 200 * 1024) buffers = 4;
+    a.share = buffers == 4;
+    size_t smem = mm_smem_bytes(d, dv, alias, buffers);
+    int bn = mm_key_tile(d, dv, alias);
     if (alias) {
-        if (slice <= 64) mm_launch<8, true>(a, grid, smem, stream);
-        else if (slice <= 128) mm_launch<16, true>(a, grid, smem, stream);
-        else mm_launch<32, true>(a, grid, smem, stream);
+        if (slice <= 64) mm_launch_bn<8, true>(a, bn, grid, smem, stream);
+        else mm_launch_bn<16, true>(a, bn, grid, smem, stream);
     } else {
-        if (slice <= 64) mm_launch<8, false>(a, grid, smem, stream);
-        else if (slice <= 128) mm_launch<16, false>(a, grid, smem, stream);
-        else mm_launch<32, false>(a, grid, smem, stream);
+        if (slice <= 64) mm_launch_bn<8, false>(a, bn, grid, smem, stream);
+        else mm_launch_bn<16, false>(a, bn, grid, smem, stream);
     }
     return ce_check_launch("ce_masked_attention_mma");
 }

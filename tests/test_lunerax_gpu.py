@@ -106,6 +106,17 @@ def test_product_per_head_with_gate_and_value_blend_kernels():
         ops.head_matmul(x.cuda()[:, 3:], K, w.cuda(), out, N, H, N, K, gate=gate.cuda()[:, 4:])
         want_g = want * torch.sigmoid(gate[:, 4:].double()).reshape(T, H, N)
         assert rel_err(out.cpu().numpy(), want_g.reshape(T, -1).numpy()) < 1e-5
+    # bfloat16 with sizes in multiples of 16: the tensor-core form, with a ragged last tile of tokens and of outputs
+    ops.reset_kernel_counts()
+    for T, H, N, K in ((70, 3, 48, 32), (5, 2, 128, 80), (130, 1, 16, 16)):
+        x = torch.randn(T, H * K, generator=g).cuda().bfloat16()
+        w = (torch.randn(H, N, K, generator=g) * 0.3).cuda().bfloat16()
+        gate = torch.randn(T, H * N, generator=g).cuda()
+        want = torch.einsum("thk,hnk->thn", x.double().reshape(T, H, K), w.double()) * torch.sigmoid(gate.double()).reshape(T, H, N)
+        out = torch.zeros(T, H * N, device="cuda", dtype=torch.bfloat16)
+        ops.head_matmul(x, K, w, out, N, H, N, K, gate=gate)
+        assert rel_err(out.float().cpu().numpy(), want.reshape(T, -1).cpu().numpy()) < 1e-2
+    assert ops.kernel_counts().get("head_matmul_wmma_kernel") == 3
     rows, first = torch.randn(6, 30, generator=g), torch.randn(6, 25, generator=g)
     rd = rows.cuda()
     ops.value_mix(rd, 8, 12, first.cuda(), 5, 0.3)
