@@ -18,14 +18,15 @@
 //   finish      every (token, head): root mean square, weight, gate, one rounding at the store   (parallel)
 //
 // The columns of S (value channels) are independent of one another, so a slice of GD_COLS columns is a block of
-// its own and a column lives in the registers of GD_R neighbouring lanes; the two sums over rows a token needs
+// its own and a column lives in the registers of 16 neighbouring lanes (32 for more than 128 key channels, so that a
+// thread holds at most 8 rows); the two sums over rows a token needs
 // are a per-thread run plus a butterfly over those lanes: the order of every sum depends on d only, never on
-// how the tokens were cut into steps or on the batch.
+// how the tokens were cut into steps or on the batch.  The decay is applied as S^T (k * g) for the dot product and
+// as g * S + k u for the new state, which is the same arithmetic as decaying first, term by term.
 #include "common.cuh"
 
-#define GD_R 16                  // lanes that share a column of the state
 #define GD_COLS 8                // value channels a block walks
-#define GD_TILE 16               // tokens a buffer holds (at most GD_R: lane g of a column stores token g's output)
+#define GD_TILE 16               // tokens a buffer holds (at most the lanes of a column: lane g stores token g's output)
 
 __device__ __forceinline__ float gd_sigmoid(float z) { return 1.0f / (1.0f + expf(-z)); }
 __device__ __forceinline__ float gd_softplus(float z) { return z > 20.f ? z : log1pf(expf(z)); }
@@ -154,22 +155,31 @@ __device__ __forceinline__ void gd_stage(const GatedDeltaArgs& a, float* buf, in
     asm volatile("cp.async.commit_group;" ::: "memory");
 }
 
-template <int RPT, bool VEC>
+// A thread's rows: for m < RPT / 4 the four rows (m * GD_R + g) * 4 .. + 3, so that the lanes of a column read
+// consecutive float4 of a staged vector at a time (no bank conflicts; the other column of the warp reads the same
+// addresses).  What a token's step costs is the chain of instructions that depend on the state: the staged vectors of the
+// NEXT token are read, and k * decay formed, while the current token's sums travel over the lanes; the decayed state
+// decay * S is formed beside the dot product (k * decay)^T S of the old state instead of before it; the read-out q^T S is
+// off the chain altogether.
+template <int RPT, bool VEC, int GD_R>
 __global__ void __launch_bounds__(GD_R * GD_COLS) gated_delta_walk_kernel(GatedDeltaArgs a) {
     ce_pdl_begin();
     extern __shared__ __align__(16) float gd_smem[];
+    constexpr int R4 = RPT / 4;
     int d = a.d, dv = a.dv;
     int h = blockIdx.x, b = blockIdx.y, col0 = blockIdx.z * GD_COLS, tid = threadIdx.x;
     int t_begin = a.q_start[b], t_end = a.q_start[b + 1];
     if (t_end <= t_begin) return;
     int ncols = min(GD_COLS, dv - col0);
     int jj = tid / GD_R, g = tid % GD_R, j = col0 + jj;
-    int i0 = g * RPT;                         // this thread's rows: i0 .. i0 + RPT - 1 (RPT is a multiple of 4)
     bool owner = jj < ncols;
     float* sp = a.state + ((size_t)a.seq_slot[b] * a.H + h) * d * dv;
     float S[RPT];
 #pragma unroll
-    for (int m = 0; m < RPT; ++m) S[m] = (owner && i0 + m < d) ? sp[(size_t)(i0 + m) * dv + j] : 0.f;
+    for (int m = 0; m < RPT; ++m) {
+        int row = ((m >> 2) * GD_R + g) * 4 + (m & 3);
+        S[m] = (owner && row < d) ? sp[(size_t)row * dv + j] : 0.f;
+    }
     // a row of the staged vectors is padded to GD_R * RPT floats, so that every thread reads whole float4
     constexpr int dp = GD_R * RPT;
     int buf_floats = 3 * GD_TILE * dp + GD_TILE * (GD_COLS + 1);
@@ -192,24 +202,40 @@ __global__ void __launch_bounds__(GD_R * GD_COLS) gated_delta_walk_kernel(GatedD
         // The sum over rows of S^T q is not needed by the next token: every thread keeps its part for each token of
         // the tile, and the butterflies of all tokens run together after the walk (their latencies overlap).
         float part[GD_TILE];
+        float4 w[R4], kw[R4], k[R4], q[R4];
+        float vj, beta;
+        auto fetch = [&](int tok) {                 // a token's vectors; nothing here depends on the state
+#pragma unroll
+            for (int m = 0; m < R4; ++m) {
+                w[m] = *reinterpret_cast<const float4*>(buf + (0 * GD_TILE + tok) * dp + (m * GD_R + g) * 4);
+                k[m] = *reinterpret_cast<const float4*>(buf + (1 * GD_TILE + tok) * dp + (m * GD_R + g) * 4);
+                q[m] = *reinterpret_cast<const float4*>(buf + (2 * GD_TILE + tok) * dp + (m * GD_R + g) * 4);
+                kw[m] = make_float4(k[m].x * w[m].x, k[m].y * w[m].y, k[m].z * w[m].z, k[m].w * w[m].w);
+            }
+            vj = owner ? vbuf[tok * (GD_COLS + 1) + jj] : 0.f;
+            beta = vbuf[tok * (GD_COLS + 1) + GD_COLS];
+        };
+        fetch(0);
 #pragma unroll
         for (int tok = 0; tok < GD_TILE; ++tok) {
             part[tok] = 0.f;
             if (tok < n_tok) {
-                const float4* w_ = reinterpret_cast<const float4*>(buf + (0 * GD_TILE + tok) * dp + i0);
-                const float4* k_ = reinterpret_cast<const float4*>(buf + (1 * GD_TILE + tok) * dp + i0);
-                const float4* q_ = reinterpret_cast<const float4*>(buf + (2 * GD_TILE + tok) * dp + i0);
-                // the decay, and k^T (decayed S) over this thread's rows in four runs (a fixed order)
+                // (k * decay)^T S over this thread's rows in four runs (a fixed order), and the decayed state beside it
                 float p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;
+                float dS[RPT];
+                float4 kc[R4], qc[R4];
 #pragma unroll
-                for (int m = 0; m < RPT / 4; ++m) {
-                    float4 w = w_[m], k = k_[m];
-                    S[4 * m] *= w.x; S[4 * m + 1] *= w.y; S[4 * m + 2] *= w.z; S[4 * m + 3] *= w.w;
-                    p0 = fmaf(k.x, S[4 * m], p0); p1 = fmaf(k.y, S[4 * m + 1], p1);
-                    p2 = fmaf(k.z, S[4 * m + 2], p2); p3 = fmaf(k.w, S[4 * m + 3], p3);
+                for (int m = 0; m < R4; ++m) {
+                    p0 = fmaf(kw[m].x, S[4 * m], p0); p1 = fmaf(kw[m].y, S[4 * m + 1], p1);
+                    p2 = fmaf(kw[m].z, S[4 * m + 2], p2); p3 = fmaf(kw[m].w, S[4 * m + 3], p3);
+                    dS[4 * m] = w[m].x * S[4 * m]; dS[4 * m + 1] = w[m].y * S[4 * m + 1];
+                    dS[4 * m + 2] = w[m].z * S[4 * m + 2]; dS[4 * m + 3] = w[m].w * S[4 * m + 3];
+                    kc[m] = k[m]; qc[m] = q[m];
                 }
                 float dot = (p0 + p1) + (p2 + p3);
-                // over the column's sixteen lanes in two rounds of four: every lane adds the same pairs, so all hold the same sum
+                const float v_now = vj, beta_now = beta;
+                if (tok + 1 < GD_TILE) fetch(tok + 1);          // (rows past the tile's tokens hold zeros or older tokens: unused)
+                // over the column's lanes in rounds of four: every lane adds the same pairs, so all hold the same sum
                 {
                     float e1 = __shfl_xor_sync(0xffffffffu, dot, 1), e2 = __shfl_xor_sync(0xffffffffu, dot, 2),
                           e3 = __shfl_xor_sync(0xffffffffu, dot, 3);
@@ -217,17 +243,16 @@ __global__ void __launch_bounds__(GD_R * GD_COLS) gated_delta_walk_kernel(GatedD
                     float f1 = __shfl_xor_sync(0xffffffffu, dot, 4), f2 = __shfl_xor_sync(0xffffffffu, dot, 8),
                           f3 = __shfl_xor_sync(0xffffffffu, dot, 12);
                     dot = (dot + f1) + (f2 + f3);
+                    if (GD_R == 32) dot += __shfl_xor_sync(0xffffffffu, dot, 16);
                 }
-                float vj = owner ? vbuf[tok * (GD_COLS + 1) + jj] : 0.f;
-                float u = vbuf[tok * (GD_COLS + 1) + GD_COLS] * (vj - dot);
+                float u = beta_now * (v_now - dot);
                 float q0 = 0.f, q1 = 0.f, q2 = 0.f, q3 = 0.f;
 #pragma unroll
-                for (int m = 0; m < RPT / 4; ++m) {
-                    float4 k = k_[m], q = q_[m];
-                    float s0 = fmaf(k.x, u, S[4 * m]), s1 = fmaf(k.y, u, S[4 * m + 1]);
-                    float s2 = fmaf(k.z, u, S[4 * m + 2]), s3 = fmaf(k.w, u, S[4 * m + 3]);
+                for (int m = 0; m < R4; ++m) {
+                    float s0 = fmaf(kc[m].x, u, dS[4 * m]), s1 = fmaf(kc[m].y, u, dS[4 * m + 1]);
+                    float s2 = fmaf(kc[m].z, u, dS[4 * m + 2]), s3 = fmaf(kc[m].w, u, dS[4 * m + 3]);
                     S[4 * m] = s0; S[4 * m + 1] = s1; S[4 * m + 2] = s2; S[4 * m + 3] = s3;
-                    q0 = fmaf(s0, q.x, q0); q1 = fmaf(s1, q.y, q1); q2 = fmaf(s2, q.z, q2); q3 = fmaf(s3, q.w, q3);
+                    q0 = fmaf(s0, qc[m].x, q0); q1 = fmaf(s1, qc[m].y, q1); q2 = fmaf(s2, qc[m].z, q2); q3 = fmaf(s3, qc[m].w, q3);
                 }
                 part[tok] = (q0 + q1) + (q2 + q3);
             }
@@ -244,8 +269,10 @@ __global__ void __launch_bounds__(GD_R * GD_COLS) gated_delta_walk_kernel(GatedD
         __syncthreads();             // the buffer is free for the tile after the next
     }
 #pragma unroll
-    for (int m = 0; m < RPT; ++m)
-        if (owner && i0 + m < d) sp[(size_t)(i0 + m) * dv + j] = S[m];
+    for (int m = 0; m < RPT; ++m) {
+        int row = ((m >> 2) * GD_R + g) * 4 + (m & 3);
+        if (owner && row < d) sp[(size_t)row * dv + j] = S[m];
+    }
 }
 
 // One block per token, a warp per head in turn: root mean square over the head's values, weight, gate.
@@ -268,18 +295,18 @@ __global__ void gated_delta_finish_kernel(GatedDeltaArgs a) {
     }
 }
 
-template <int RPT>
+template <int RPT, int R>
 static void gd_launch_walk(const GatedDeltaArgs& a, int B, bool vec, cudaStream_t stream) {
-    size_t floats = 3 * GD_TILE * GD_R * RPT + GD_TILE * (GD_COLS + 1);
+    size_t floats = 3 * GD_TILE * R * RPT + GD_TILE * (GD_COLS + 1);
     size_t smem = (size_t)2 * ((floats + 3) / 4 * 4) * sizeof(float);
     dim3 grid(a.H, B, (a.dv + GD_COLS - 1) / GD_COLS);
     ce_note("gated_delta_walk_kernel");
     if (vec) {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(gated_delta_walk_kernel<RPT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        ce_launch(gated_delta_walk_kernel<RPT, true>, grid, GD_R * GD_COLS, smem, stream, a);
+        if (smem > 48 * 1024) cudaFuncSetAttribute(gated_delta_walk_kernel<RPT, true, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        ce_launch(gated_delta_walk_kernel<RPT, true, R>, grid, R * GD_COLS, smem, stream, a);
     } else {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(gated_delta_walk_kernel<RPT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        ce_launch(gated_delta_walk_kernel<RPT, false>, grid, GD_R * GD_COLS, smem, stream, a);
+        if (smem > 48 * 1024) cudaFuncSetAttribute(gated_delta_walk_kernel<RPT, false, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        ce_launch(gated_delta_walk_kernel<RPT, false, R>, grid, R * GD_COLS, smem, stream, a);
     }
 }
 
@@ -325,10 +352,12 @@ extern "C" int ce_gated_delta(const float* proj, const float* dec, const float* 
         // 16-byte copies where every source address is a multiple of 16
         int C = 2 * G * d + H * dv;
         bool vec = d % 4 == 0 && C % 4 == 0 && ((uintptr_t)prep & 15) == 0;
-        int rpt = (d + GD_R - 1) / GD_R;
-        if (rpt <= 4) gd_launch_walk<4>(a, B, vec, stream);
-        else if (rpt <= 8) gd_launch_walk<8>(a, B, vec, stream);
-        else gd_launch_walk<16>(a, B, vec, stream);
+        // lanes a column and rows a thread by the key size alone (never by the batch: a request's sums do not depend on its neighbours)
+        // Measured at 2,048 tokens with heads of 128 x 128: 16 lanes a column took 0.63 ms (16 heads) and 0.90 ms (32 heads) a
+        // launch, 32 lanes 0.61 and 1.21: twice the warps for the same columns, and with 32 heads the SMs' issue slots run out.
+        if (d <= 64) gd_launch_walk<4, 16>(a, B, vec, stream);
+        else if (d <= 128) gd_launch_walk<8, 16>(a, B, vec, stream);
+        else gd_launch_walk<8, 32>(a, B, vec, stream);
     }
     return ce_check_launch("ce_gated_delta");
 }
