@@ -90,6 +90,9 @@ SINGLE = {
     "latent": config([latent()], side=0, logit_cap=0),
     "delta": config([delta()], side=0, logit_cap=0),
     "delta_one_tap": config([delta(conv=1, heads=2, kv_heads=2, dim=36, vdim=5)], side=0, logit_cap=0),
+    # more than 128 key channels (32 lanes a state column), and sizes that are no multiples of 4 (4-byte copies)
+    "delta_wide_keys": config([delta(heads=1, kv_heads=1, dim=136, vdim=8, conv=2, a_rank=4, g_rank=4)], side=0, logit_cap=0),
+    "delta_odd_sizes": config([delta(heads=2, kv_heads=1, dim=10, vdim=7, conv=3, a_rank=3, g_rank=2)], width=34, side=0, logit_cap=0),
     "feed_forward_and_side": config([attention(ff=56, heads=1, kv_heads=1)], side=7, logit_cap=3.0),
 }
 
