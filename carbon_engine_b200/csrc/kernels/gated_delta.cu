@@ -51,10 +51,13 @@ struct GatedDeltaArgs {
     float eps;
 };
 
-// One block per token.  A warp per head of q, of k (unit vectors) and of v in turn; then the decays and beta.
+// A token's heads of q, of k (unit vectors) and of v are dealt to the warps of gridDim.y blocks in turn (one block a token
+// in a long step; in a step of few tokens a block per handful of heads, so that the step is not eight blocks' work); the
+// decays and beta are dealt the same way.
 __global__ void gated_delta_prepare_kernel(GatedDeltaArgs a) {
     ce_pdl_begin();
-    int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    int t = blockIdx.x, lane = threadIdx.x & 31, nwarp = (blockDim.x >> 5) * gridDim.y;
+    int warp = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
     int d = a.d, dv = a.dv, G = a.G, H = a.H, K = a.K;
     int C = 2 * G * d + H * dv;
     int b = a.seq_of_token[t];
@@ -94,9 +97,10 @@ __global__ void gated_delta_prepare_kernel(GatedDeltaArgs a) {
         for (int c = lane; c < size; c += 32) pw[c0 + c] *= inv;
     }
     float* decay = pw + C;
-    for (int e = threadIdx.x; e < H * d; e += blockDim.x)
+    int nthr = blockDim.x * gridDim.y, thr = blockIdx.y * blockDim.x + threadIdx.x;
+    for (int e = thr; e < H * d; e += nthr)
         decay[e] = expf(-expf(a.a_log[e / d]) * gd_softplus(a.dec[(size_t)t * H * d + e] + a.dt_bias[e]));
-    for (int h = threadIdx.x; h < H; h += blockDim.x) decay[H * d + h] = gd_sigmoid(a.proj[(size_t)t * a.ld + a.off_b + h]);
+    for (int h = thr; h < H; h += nthr) decay[H * d + h] = gd_sigmoid(a.proj[(size_t)t * a.ld + a.off_b + h]);
 }
 
 // One thread per (sequence, channel): the kept rows move up by the portion's length and take the portion's last inputs.
@@ -184,7 +188,12 @@ __global__ void __launch_bounds__(GD_R * GD_COLS) gated_delta_walk_kernel(GatedD
     constexpr int dp = GD_R * RPT;
     int buf_floats = 3 * GD_TILE * dp + GD_TILE * (GD_COLS + 1);
     buf_floats = (buf_floats + 3) / 4 * 4;
-    for (int e = tid; e < 2 * buf_floats; e += blockDim.x) gd_smem[e] = 0.f;       // the padding stays zero
+    // the padding of every staged row stays zero (rows of tokens a tile does not have are read ahead but never used)
+    if (dp > d)
+        for (int e = tid; e < 2 * 3 * GD_TILE * (dp - d); e += blockDim.x) {
+            int row = e / (dp - d), c = d + e % (dp - d);
+            gd_smem[(row / (3 * GD_TILE)) * buf_floats + (row % (3 * GD_TILE)) * dp + c] = 0.f;
+        }
     __syncthreads();
     int n_tiles = (t_end - t_begin + GD_TILE - 1) / GD_TILE;
     gd_stage<dp, VEC>(a, gd_smem, t_begin, min(GD_TILE, t_end - t_begin), h, col0, ncols);
@@ -337,7 +346,9 @@ extern "C" int ce_gated_delta(const float* proj, const float* dec, const float* 
     int threads = heads >= 8 ? 256 : 32 * heads;
     if (stage == 1) {
         ce_note("gated_delta_prepare_kernel");
-        ce_launch(gated_delta_prepare_kernel, T, threads, 0, stream, a);
+        int per_block = threads / 32, want = (heads + per_block - 1) / per_block, room = 4 * 148 / T;
+        int split = want < room ? want : room;
+        ce_launch(gated_delta_prepare_kernel, dim3(T, split < 1 ? 1 : split), threads, 0, stream, a);
     } else if (stage == 2) {
         if (K == 1) return CE_OK;
         size_t total = (size_t)B * (2 * G * d + H * dv), want = (total + 255) / 256;

@@ -41,11 +41,63 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const float* __res
     }
 }
 
+// The same with float4 loads for widths in multiples of 4 up to 4 * 1024 * LNV_MAX: a thread keeps its float4s in registers.
+#define LNV_MAX 4
+template <typename T>
+__global__ void layernorm_vec_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b,
+                                     T* __restrict__ out, const int* __restrict__ rows, int H, float eps) {
+    ce_pdl_begin();
+    __shared__ float scratch[32];
+    int r = blockIdx.x, H4 = H >> 2;
+    const float4* xr = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * H);
+    float4 v[LNV_MAX];
+    float s = 0.f;
+#pragma unroll
+    for (int n = 0; n < LNV_MAX; ++n) {
+        int j = threadIdx.x + n * blockDim.x;
+        v[n] = j < H4 ? xr[j] : make_float4(0.f, 0.f, 0.f, 0.f);
+        s += (v[n].x + v[n].y) + (v[n].z + v[n].w);
+    }
+    float mean = ce_block_sum(s, scratch) / (float)H;
+    float q = 0.f;
+#pragma unroll
+    for (int n = 0; n < LNV_MAX; ++n) {
+        int j = threadIdx.x + n * blockDim.x;
+        if (j < H4) {
+            v[n].x -= mean; v[n].y -= mean; v[n].z -= mean; v[n].w -= mean;
+            q += (v[n].x * v[n].x + v[n].y * v[n].y) + (v[n].z * v[n].z + v[n].w * v[n].w);
+        }
+    }
+    float inv = 1.0f / sqrtf(ce_block_sum(q, scratch) / (float)H + eps);
+    const float4* w4 = reinterpret_cast<const float4*>(w);
+    const float4* b4 = reinterpret_cast<const float4*>(b);
+#pragma unroll
+    for (int n = 0; n < LNV_MAX; ++n) {
+        int j = threadIdx.x + n * blockDim.x;
+        if (j < H4) {
+            float4 ww = w4[j], bb = b4[j];
+            T* o = out + (size_t)r * H + 4 * j;
+            CeType<T>::store(o, v[n].x * inv * ww.x + bb.x); CeType<T>::store(o + 1, v[n].y * inv * ww.y + bb.y);
+            CeType<T>::store(o + 2, v[n].z * inv * ww.z + bb.z); CeType<T>::store(o + 3, v[n].w * inv * ww.w + bb.w);
+        }
+    }
+}
+
 extern "C" int ce_layernorm(const float* x, const float* w, const float* b, void* out, int out_dtype, const int* rows,
                             int R, int H, float eps, cudaStream_t stream) {
     if (R == 0) return CE_OK;
     if (!x || !w || !b || !out) return ce_fail(CE_ERR_ARG, "ce_layernorm: null pointer");
     if (H <= 0) return ce_fail(CE_ERR_SIZE, "ce_layernorm: width %d", H);
+    if (out_dtype != CE_F32 && out_dtype != CE_BF16) return ce_fail(CE_ERR_ARG, "ce_layernorm: unknown dtype %d", out_dtype);
+    if (H % 4 == 0 && H >= 256 && ((((uintptr_t)x | (uintptr_t)w | (uintptr_t)b) & 15) == 0)) {
+        int H4 = H / 4, vt = H4 >= 2048 ? 1024 : H4 >= 512 ? 512 : H4 >= 256 ? 256 : 128;
+        if (H4 <= vt * LNV_MAX) {
+            ce_note("layernorm_vec_kernel");
+            if (out_dtype == CE_F32) ce_launch(layernorm_vec_kernel<float>, R, vt, 0, stream, x, w, b, (float*)out, rows, H, eps);
+            else ce_launch(layernorm_vec_kernel<__nv_bfloat16>, R, vt, 0, stream, x, w, b, (__nv_bfloat16*)out, rows, H, eps);
+            return ce_check_launch("ce_layernorm");
+        }
+    }
     int threads = H >= 4096 ? 512 : H >= 1024 ? 256 : 128;
     ce_note("layernorm_kernel");
     if (out_dtype == CE_F32) ce_launch(layernorm_kernel<float>, R, threads, 0, stream, x, w, b, (float*)out, rows, H, eps);
