@@ -166,7 +166,7 @@ __device__ __forceinline__ void gd_stage(const GatedDeltaArgs& a, float* buf, in
 // decay * S is formed beside the dot product (k * decay)^T S of the old state instead of before it; the read-out q^T S is
 // off the chain altogether.
 template <int RPT, bool VEC, int GD_R>
-__global__ void __launch_bounds__(GD_R * GD_COLS) gated_delta_walk_kernel(GatedDeltaArgs a) {
+__global__ void __launch_bounds__(GD_R * GD_COLS) gated_delta_walk_kernel(GatedDeltaArgs a, int n_buf) {
     ce_pdl_begin();
     extern __shared__ __align__(16) float gd_smem[];
     constexpr int R4 = RPT / 4;
@@ -190,7 +190,7 @@ __global__ void __launch_bounds__(GD_R * GD_COLS) gated_delta_walk_kernel(GatedD
     buf_floats = (buf_floats + 3) / 4 * 4;
     // the padding of every staged row stays zero (rows of tokens a tile does not have are read ahead but never used)
     if (dp > d)
-        for (int e = tid; e < 2 * 3 * GD_TILE * (dp - d); e += blockDim.x) {
+        for (int e = tid; e < n_buf * 3 * GD_TILE * (dp - d); e += blockDim.x) {
             int row = e / (dp - d), c = d + e % (dp - d);
             gd_smem[(row / (3 * GD_TILE)) * buf_floats + (row % (3 * GD_TILE)) * dp + c] = 0.f;
         }
@@ -199,11 +199,12 @@ __global__ void __launch_bounds__(GD_R * GD_COLS) gated_delta_walk_kernel(GatedD
     gd_stage<dp, VEC>(a, gd_smem, t_begin, min(GD_TILE, t_end - t_begin), h, col0, ncols);
     for (int tile = 0; tile < n_tiles; ++tile) {
         int t0 = t_begin + tile * GD_TILE, n_tok = min(GD_TILE, t_end - t0);
-        float* buf = gd_smem + (tile & 1) * buf_floats;
-        if (tile + 1 < n_tiles) {
+        float* buf = gd_smem + (tile & (n_buf - 1)) * buf_floats;
+        if (tile + 1 < n_tiles && n_buf == 2) {
             gd_stage<dp, VEC>(a, gd_smem + ((tile + 1) & 1) * buf_floats, t0 + GD_TILE, min(GD_TILE, t_end - t0 - GD_TILE), h, col0, ncols);
             asm volatile("cp.async.wait_group 1;" ::: "memory");
         } else {
+            if (tile > 0 && n_buf == 1) gd_stage<dp, VEC>(a, buf, t0, n_tok, h, col0, ncols);     // one buffer: a tile is staged when its turn comes
             asm volatile("cp.async.wait_group 0;" ::: "memory");
         }
         __syncthreads();
@@ -284,11 +285,12 @@ __global__ void __launch_bounds__(GD_R * GD_COLS) gated_delta_walk_kernel(GatedD
     }
 }
 
-// One block per token, a warp per head in turn: root mean square over the head's values, weight, gate.
+// A token's heads are dealt to the warps of gridDim.y blocks in turn: root mean square over the head's values, weight, gate.
 template <typename T>
 __global__ void gated_delta_finish_kernel(GatedDeltaArgs a) {
     ce_pdl_begin();
-    int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    int t = blockIdx.x, lane = threadIdx.x & 31, nwarp = (blockDim.x >> 5) * gridDim.y;
+    int warp = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
     int dv = a.dv, n = a.H * dv;
     const float* o = a.raw + (size_t)t * n;
     const float* gz = a.gz + (size_t)t * n;
@@ -304,18 +306,19 @@ __global__ void gated_delta_finish_kernel(GatedDeltaArgs a) {
     }
 }
 
+// n_buf 1: a step of single tokens (every sequence has one tile): one staging buffer, twice the blocks an SM
 template <int RPT, int R>
-static void gd_launch_walk(const GatedDeltaArgs& a, int B, bool vec, cudaStream_t stream) {
+static void gd_launch_walk(const GatedDeltaArgs& a, int B, bool vec, int n_buf, cudaStream_t stream) {
     size_t floats = 3 * GD_TILE * R * RPT + GD_TILE * (GD_COLS + 1);
-    size_t smem = (size_t)2 * ((floats + 3) / 4 * 4) * sizeof(float);
+    size_t smem = (size_t)n_buf * ((floats + 3) / 4 * 4) * sizeof(float);
     dim3 grid(a.H, B, (a.dv + GD_COLS - 1) / GD_COLS);
     ce_note("gated_delta_walk_kernel");
     if (vec) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(gated_delta_walk_kernel<RPT, true, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        ce_launch(gated_delta_walk_kernel<RPT, true, R>, grid, R * GD_COLS, smem, stream, a);
+        ce_launch(gated_delta_walk_kernel<RPT, true, R>, grid, R * GD_COLS, smem, stream, a, n_buf);
     } else {
         if (smem > 48 * 1024) cudaFuncSetAttribute(gated_delta_walk_kernel<RPT, false, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        ce_launch(gated_delta_walk_kernel<RPT, false, R>, grid, R * GD_COLS, smem, stream, a);
+        ce_launch(gated_delta_walk_kernel<RPT, false, R>, grid, R * GD_COLS, smem, stream, a, n_buf);
     }
 }
 
@@ -357,8 +360,10 @@ extern "C" int ce_gated_delta(const float* proj, const float* dec, const float* 
     } else if (stage == 4) {
         ce_note("gated_delta_finish_kernel");
         int th = H >= 8 ? 256 : 32 * H;
-        if (out_dtype == CE_F32) ce_launch(gated_delta_finish_kernel<float>, T, th, 0, stream, a);
-        else ce_launch(gated_delta_finish_kernel<__nv_bfloat16>, T, th, 0, stream, a);
+        int want = (H + th / 32 - 1) / (th / 32), room = 4 * 148 / T, split = want < room ? want : room;
+        dim3 grid(T, split < 1 ? 1 : split);
+        if (out_dtype == CE_F32) ce_launch(gated_delta_finish_kernel<float>, grid, th, 0, stream, a);
+        else ce_launch(gated_delta_finish_kernel<__nv_bfloat16>, grid, th, 0, stream, a);
     } else {
         // 16-byte copies where every source address is a multiple of 16
         int C = 2 * G * d + H * dv;
@@ -366,9 +371,10 @@ extern "C" int ce_gated_delta(const float* proj, const float* dec, const float* 
         // lanes a column and rows a thread by the key size alone (never by the batch: a request's sums do not depend on its neighbours)
         // Measured at 2,048 tokens with heads of 128 x 128: 16 lanes a column took 0.63 ms (16 heads) and 0.90 ms (32 heads) a
         // launch, 32 lanes 0.61 and 1.21: twice the warps for the same columns, and with 32 heads the SMs' issue slots run out.
-        if (d <= 64) gd_launch_walk<4, 16>(a, B, vec, stream);
-        else if (d <= 128) gd_launch_walk<8, 16>(a, B, vec, stream);
-        else gd_launch_walk<8, 32>(a, B, vec, stream);
+        int n_buf = T == B ? 1 : 2;             // as many tokens as sequences: every sequence brings exactly one
+        if (d <= 64) gd_launch_walk<4, 16>(a, B, vec, n_buf, stream);
+        else if (d <= 128) gd_launch_walk<8, 16>(a, B, vec, n_buf, stream);
+        else gd_launch_walk<8, 32>(a, B, vec, n_buf, stream);
     }
     return ce_check_launch("ce_gated_delta");
 }

@@ -120,9 +120,45 @@ __global__ void rmsnorm_add_kernel(const float* __restrict__ y, const float* __r
     for (int j = threadIdx.x; j < H; j += blockDim.x) x[(size_t)t * H + j] += yr[j] * inv * w[j];
 }
 
+// The same with float4 loads, y kept in registers between the two passes (widths in multiples of 4 up to 4 * threads * LNV_MAX)
+__global__ void rmsnorm_add_vec_kernel(const float* __restrict__ y, const float* __restrict__ w, float* __restrict__ x, int H, float eps) {
+    ce_pdl_begin();
+    __shared__ float scratch[32];
+    int t = blockIdx.x, H4 = H >> 2;
+    const float4* yr = reinterpret_cast<const float4*>(y + (size_t)t * H);
+    float4 v[LNV_MAX];
+    float q = 0.f;
+#pragma unroll
+    for (int n = 0; n < LNV_MAX; ++n) {
+        int j = threadIdx.x + n * blockDim.x;
+        v[n] = j < H4 ? yr[j] : make_float4(0.f, 0.f, 0.f, 0.f);
+        q += (v[n].x * v[n].x + v[n].y * v[n].y) + (v[n].z * v[n].z + v[n].w * v[n].w);
+    }
+    float inv = 1.0f / sqrtf(ce_block_sum(q, scratch) / (float)H + eps);
+    float4* xr = reinterpret_cast<float4*>(x + (size_t)t * H);
+    const float4* w4 = reinterpret_cast<const float4*>(w);
+#pragma unroll
+    for (int n = 0; n < LNV_MAX; ++n) {
+        int j = threadIdx.x + n * blockDim.x;
+        if (j < H4) {
+            float4 xv = xr[j], ww = w4[j];
+            xv.x += v[n].x * inv * ww.x; xv.y += v[n].y * inv * ww.y; xv.z += v[n].z * inv * ww.z; xv.w += v[n].w * inv * ww.w;
+            xr[j] = xv;
+        }
+    }
+}
+
 extern "C" int ce_rmsnorm_add(const float* y, const float* w, float* x, int T, int H, float eps, cudaStream_t stream) {
     if (T == 0) return CE_OK;
     if (!y || !w || !x) return ce_fail(CE_ERR_ARG, "ce_rmsnorm_add: null pointer");
+    if (H % 4 == 0 && H >= 256 && ((((uintptr_t)x | (uintptr_t)w | (uintptr_t)y) & 15) == 0)) {
+        int H4 = H / 4, vt = H4 >= 2048 ? 1024 : H4 >= 512 ? 512 : H4 >= 256 ? 256 : 128;
+        if (H4 <= vt * LNV_MAX) {
+            ce_note("rmsnorm_add_vec_kernel");
+            ce_launch(rmsnorm_add_vec_kernel, T, vt, 0, stream, y, w, x, H, eps);
+            return ce_check_launch("ce_rmsnorm_add");
+        }
+    }
     ce_note("rmsnorm_add_kernel");
     ce_launch(rmsnorm_add_kernel, T, H >= 4096 ? 512 : H >= 1024 ? 256 : 128, 0, stream, y, w, x, H, eps);
     return ce_check_launch("ce_rmsnorm_add");

@@ -224,12 +224,15 @@ __global__ void __launch_bounds__(256) head_matmul_kernel(const T* __restrict__ 
 // The same product in bfloat16 on the tensor cores (wmma m16n16k16, float32 sums): a block of four warps takes 64 tokens x 64
 // outputs of one head; the tokens' rows go through shared memory 64 elements of K at a time (rows past the last token are
 // zeros), the weights' fragments come straight from memory (W[h] is [N, K] row-major, that is K x N column-major with
-// leading dimension K).  Wants N and K in multiples of 16 and rows that start on 32-byte boundaries.
+// leading dimension K).  Wants N and K in multiples of 16 and rows that start on 32-byte boundaries.  With at most 16 tokens
+// (FEW) the four warps take the four 16-column parts of the block's outputs for the same 16 rows instead of 16 rows each: a
+// warp then walks K with one weight fragment a step instead of four, and its chain of loads is a quarter as long.
 #include <mma.h>
 #define HW_TM 64
 #define HW_TN 64
 #define HW_TK 64
 
+template <bool FEW>
 __global__ void __launch_bounds__(128) head_matmul_wmma_kernel(const __nv_bfloat16* __restrict__ in, int in_stride, int in_head,
                                                                const __nv_bfloat16* __restrict__ W, __nv_bfloat16* __restrict__ out,
                                                                int out_stride, int out_head, const float* __restrict__ gate,
@@ -241,12 +244,14 @@ __global__ void __launch_bounds__(128) head_matmul_wmma_kernel(const __nv_bfloat
     int h = blockIdx.z, m0 = blockIdx.y * HW_TM, n0 = blockIdx.x * HW_TN, tid = threadIdx.x, warp = tid >> 5;
     const __nv_bfloat16* Wh = W + (size_t)h * N * K;
     int n_frag = min(HW_TN, N - n0) / 16;
-    wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc[HW_TN / 16];
+    constexpr int NF = FEW ? 1 : HW_TN / 16;              // fragments a warp holds
+    const int wrow = FEW ? 0 : warp * 16, f0 = FEW ? warp : 0;
+    wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc[NF];
 #pragma unroll
-    for (int j = 0; j < HW_TN / 16; ++j) wmma::fill_fragment(acc[j], 0.f);
+    for (int j = 0; j < NF; ++j) wmma::fill_fragment(acc[j], 0.f);
     for (int k0 = 0; k0 < K; k0 += HW_TK) {
         int kw = min(HW_TK, K - k0);                      // a multiple of 16
-        for (int e = tid; e < HW_TM * (HW_TK / 8); e += 128) {
+        for (int e = tid; e < (FEW ? 16 : HW_TM) * (HW_TK / 8); e += 128) {
             int r = e / (HW_TK / 8), c = (e % (HW_TK / 8)) * 8;
             uint4 v = make_uint4(0u, 0u, 0u, 0u);
             if (m0 + r < M && c < kw) v = *reinterpret_cast<const uint4*>(in + (size_t)(m0 + r) * in_stride + (size_t)h * in_head + k0 + c);
@@ -255,12 +260,12 @@ __global__ void __launch_bounds__(128) head_matmul_wmma_kernel(const __nv_bfloat
         __syncthreads();
         for (int kk = 0; kk < kw; kk += 16) {
             wmma::fragment<wmma::matrix_a, 16, 16, 16, __nv_bfloat16, wmma::row_major> fa;
-            wmma::load_matrix_sync(fa, &As[warp * 16][kk], HW_TK + 16);
+            wmma::load_matrix_sync(fa, &As[wrow][kk], HW_TK + 16);
 #pragma unroll
-            for (int j = 0; j < HW_TN / 16; ++j) {
-                if (j < n_frag) {
+            for (int j = 0; j < NF; ++j) {
+                if (f0 + j < n_frag) {
                     wmma::fragment<wmma::matrix_b, 16, 16, 16, __nv_bfloat16, wmma::col_major> fb;
-                    wmma::load_matrix_sync(fb, Wh + (size_t)(n0 + j * 16) * K + k0 + kk, K);
+                    wmma::load_matrix_sync(fb, Wh + (size_t)(n0 + (f0 + j) * 16) * K + k0 + kk, K);
                     wmma::mma_sync(acc[j], fa, fb, acc[j]);
                 }
             }
@@ -268,10 +273,10 @@ __global__ void __launch_bounds__(128) head_matmul_wmma_kernel(const __nv_bfloat
         __syncthreads();
     }
 #pragma unroll
-    for (int j = 0; j < HW_TN / 16; ++j)
-        if (j < n_frag) wmma::store_matrix_sync(&Cs[warp * 16][j * 16], acc[j], HW_TN + 8, wmma::mem_row_major);
+    for (int j = 0; j < NF; ++j)
+        if (f0 + j < n_frag) wmma::store_matrix_sync(&Cs[wrow][(f0 + j) * 16], acc[j], HW_TN + 8, wmma::mem_row_major);
     __syncthreads();
-    for (int e = tid; e < HW_TM * (HW_TN / 2); e += 128) {
+    for (int e = tid; e < (FEW ? 16 : HW_TM) * (HW_TN / 2); e += 128) {
         int r = e / (HW_TN / 2), c = (e % (HW_TN / 2)) * 2;
         int m = m0 + r, n = n0 + c;
         if (m >= M || n >= N) continue;
@@ -295,8 +300,12 @@ extern "C" int ce_head_matmul(const void* in, int in_stride, int in_head, const 
         out_head % 2 == 0 && (((uintptr_t)in | (uintptr_t)W) & 31) == 0 && (((uintptr_t)out) & 3) == 0) {
         dim3 grid((N + HW_TN - 1) / HW_TN, (M + HW_TM - 1) / HW_TM, H);
         ce_note("head_matmul_wmma_kernel");
-        ce_launch(head_matmul_wmma_kernel, grid, 128, 0, stream, (const __nv_bfloat16*)in, in_stride, in_head, (const __nv_bfloat16*)W,
-                  (__nv_bfloat16*)out, out_stride, out_head, gate, gate_stride, M, N, K);
+        if (M <= 16)
+            ce_launch(head_matmul_wmma_kernel<true>, grid, 128, 0, stream, (const __nv_bfloat16*)in, in_stride, in_head, (const __nv_bfloat16*)W,
+                      (__nv_bfloat16*)out, out_stride, out_head, gate, gate_stride, M, N, K);
+        else
+            ce_launch(head_matmul_wmma_kernel<false>, grid, 128, 0, stream, (const __nv_bfloat16*)in, in_stride, in_head, (const __nv_bfloat16*)W,
+                      (__nv_bfloat16*)out, out_stride, out_head, gate, gate_stride, M, N, K);
         return ce_check_launch("ce_head_matmul");
     }
     dim3 grid((N + HM_TN - 1) / HM_TN, (M + HM_TM - 1) / HM_TM, H);
