@@ -214,37 +214,43 @@ __global__ void __launch_bounds__(GD_R * GD_COLS) gated_delta_walk_kernel(GatedD
         float part[GD_TILE];
         float4 w[R4], kw[R4], k[R4], q[R4];
         float vj, beta;
+        auto lo2 = [](const float4& v) { return make_float2(v.x, v.y); };
+        auto hi2 = [](const float4& v) { return make_float2(v.z, v.w); };
         auto fetch = [&](int tok) {                 // a token's vectors; nothing here depends on the state
 #pragma unroll
             for (int m = 0; m < R4; ++m) {
                 w[m] = *reinterpret_cast<const float4*>(buf + (0 * GD_TILE + tok) * dp + (m * GD_R + g) * 4);
                 k[m] = *reinterpret_cast<const float4*>(buf + (1 * GD_TILE + tok) * dp + (m * GD_R + g) * 4);
                 q[m] = *reinterpret_cast<const float4*>(buf + (2 * GD_TILE + tok) * dp + (m * GD_R + g) * 4);
-                kw[m] = make_float4(k[m].x * w[m].x, k[m].y * w[m].y, k[m].z * w[m].z, k[m].w * w[m].w);
+                float2 a0 = __fmul2_rn(lo2(k[m]), lo2(w[m])), a1 = __fmul2_rn(hi2(k[m]), hi2(w[m]));
+                kw[m] = make_float4(a0.x, a0.y, a1.x, a1.y);
             }
             vj = owner ? vbuf[tok * (GD_COLS + 1) + jj] : 0.f;
             beta = vbuf[tok * (GD_COLS + 1) + GD_COLS];
         };
         fetch(0);
+        // The arithmetic on the state runs on pairs of rows (fma.f32x2: two IEEE operations an instruction, the same results):
+        // a token's step is a chain of instructions a warp issues nearly one after another, so their number is its time.
 #pragma unroll
         for (int tok = 0; tok < GD_TILE; ++tok) {
             part[tok] = 0.f;
             if (tok < n_tok) {
                 // (k * decay)^T S over this thread's rows in four runs (a fixed order), and the decayed state beside it
-                float p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;
-                float dS[RPT];
+                float2 p01 = make_float2(0.f, 0.f), p23 = make_float2(0.f, 0.f);
+                float2 dS[RPT / 2];
                 float4 kc[R4], qc[R4];
 #pragma unroll
                 for (int m = 0; m < R4; ++m) {
-                    p0 = fmaf(kw[m].x, S[4 * m], p0); p1 = fmaf(kw[m].y, S[4 * m + 1], p1);
-                    p2 = fmaf(kw[m].z, S[4 * m + 2], p2); p3 = fmaf(kw[m].w, S[4 * m + 3], p3);
-                    dS[4 * m] = w[m].x * S[4 * m]; dS[4 * m + 1] = w[m].y * S[4 * m + 1];
-                    dS[4 * m + 2] = w[m].z * S[4 * m + 2]; dS[4 * m + 3] = w[m].w * S[4 * m + 3];
+                    float2 s01 = make_float2(S[4 * m], S[4 * m + 1]), s23 = make_float2(S[4 * m + 2], S[4 * m + 3]);
+                    p01 = __ffma2_rn(lo2(kw[m]), s01, p01);
+                    p23 = __ffma2_rn(hi2(kw[m]), s23, p23);
+                    dS[2 * m] = __fmul2_rn(lo2(w[m]), s01);
+                    dS[2 * m + 1] = __fmul2_rn(hi2(w[m]), s23);
                     kc[m] = k[m]; qc[m] = q[m];
                 }
-                float dot = (p0 + p1) + (p2 + p3);
+                float dot = (p01.x + p01.y) + (p23.x + p23.y);
                 const float v_now = vj, beta_now = beta;
-                if (tok + 1 < GD_TILE) fetch(tok + 1);          // (rows past the tile's tokens hold zeros or older tokens: unused)
+                if (tok + 1 < GD_TILE) fetch(tok + 1);          // (rows past the tile's tokens hold older tokens: unused)
                 // over the column's lanes in rounds of four: every lane adds the same pairs, so all hold the same sum
                 {
                     float e1 = __shfl_xor_sync(0xffffffffu, dot, 1), e2 = __shfl_xor_sync(0xffffffffu, dot, 2),
@@ -256,15 +262,16 @@ __global__ void __launch_bounds__(GD_R * GD_COLS) gated_delta_walk_kernel(GatedD
                     if (GD_R == 32) dot += __shfl_xor_sync(0xffffffffu, dot, 16);
                 }
                 float u = beta_now * (v_now - dot);
-                float q0 = 0.f, q1 = 0.f, q2 = 0.f, q3 = 0.f;
+                const float2 uu = make_float2(u, u);
+                float2 q01 = make_float2(0.f, 0.f), q23 = make_float2(0.f, 0.f);
 #pragma unroll
                 for (int m = 0; m < R4; ++m) {
-                    float s0 = fmaf(kc[m].x, u, dS[4 * m]), s1 = fmaf(kc[m].y, u, dS[4 * m + 1]);
-                    float s2 = fmaf(kc[m].z, u, dS[4 * m + 2]), s3 = fmaf(kc[m].w, u, dS[4 * m + 3]);
-                    S[4 * m] = s0; S[4 * m + 1] = s1; S[4 * m + 2] = s2; S[4 * m + 3] = s3;
-                    q0 = fmaf(s0, qc[m].x, q0); q1 = fmaf(s1, qc[m].y, q1); q2 = fmaf(s2, qc[m].z, q2); q3 = fmaf(s3, qc[m].w, q3);
+                    float2 s01 = __ffma2_rn(lo2(kc[m]), uu, dS[2 * m]), s23 = __ffma2_rn(hi2(kc[m]), uu, dS[2 * m + 1]);
+                    S[4 * m] = s01.x; S[4 * m + 1] = s01.y; S[4 * m + 2] = s23.x; S[4 * m + 3] = s23.y;
+                    q01 = __ffma2_rn(s01, lo2(qc[m]), q01);
+                    q23 = __ffma2_rn(s23, hi2(qc[m]), q23);
                 }
-                part[tok] = (q0 + q1) + (q2 + q3);
+                part[tok] = (q01.x + q01.y) + (q23.x + q23.y);
             }
         }
 #pragma unroll
