@@ -10,8 +10,8 @@
 // warp is a flash attention over 16 rows (S = Q K^T in float32, online softmax, P rounded to bfloat16, O += P V in
 // float32) over tiles of 64 keys that start at multiples of 64; a row's sums therefore do not depend on the tile it
 // falls in, on ``pack`` or on the batch.  Key heads may be wide (a latent row of several hundred elements), so the query
-// fragments are read from shared memory at every step instead of living in registers; value heads wider than 256 are
-// cut into slices, each a block of its own that computes the scores again.
+// fragments are read from shared memory at every step instead of living in registers; wide value heads are
+// cut into slices (of 256 for prompts, of 128 in steps of single tokens), each a block of its own that computes the scores again.
 //
 // K and V tiles come from the pages by cp.async into two buffers, a tile ahead of the arithmetic; the page of every key
 // row of a tile is looked up two tiles ahead.  Key tiles that no row of the block can see (between the kept first tokens
@@ -73,7 +73,7 @@ __device__ __forceinline__ unsigned mm_pack(float lo, float hi) {
 
 // DVT: 8-column tiles of a value slice the registers hold (slice <= 8 DVT); ALIAS: the values are the key rows' leading part
 template <int DVT, bool ALIAS, int MM_BN>
-__global__ void __launch_bounds__(MM_THREADS, 3) masked_attention_mma_kernel(MaskedMmaArgs a) {
+__global__ void __launch_bounds__(MM_THREADS, (DVT <= 16 ? 3 : 2)) masked_attention_mma_kernel(MaskedMmaArgs a) {
     ce_pdl_begin();
     extern __shared__ __align__(16) unsigned char mm_smem[];
     const int d = a.d, ldq = d + MM_PAD, ldks = d + MM_PAD;
@@ -376,28 +376,40 @@ __global__ void __launch_bounds__(MM_THREADS, 3) masked_attention_mma_kernel(Mas
     }
 }
 
-static int mm_slice(int dv) { return dv <= 128 ? dv : 128; }
-
-// keys a tile: 64, or 32 where two buffers of 64 wide key rows would leave room for one block an SM only
-static int mm_key_tile(int d, int dv, bool alias) {
-    size_t stage64 = (size_t)64 * (d + MM_PAD) + (alias ? 0 : (size_t)64 * (mm_slice(dv) + MM_PAD));
-    return ((size_t)MM_BM * (d + MM_PAD) + 2 * stage64) * sizeof(__nv_bfloat16) > 100 * 1024 ? 32 : 64;
+// Value columns a block takes: 128 at most in a step of single tokens (more blocks for the few rows), 256 at most for prompts
+// (a slice computes the scores again, so fewer slices are less arithmetic: latent attention over rows of 288 with values of
+// 256 took 480 us in two slices and 395 us in one, on 2,048 tokens; the single tokens of a decode step 61 against 80 us).
+static int mm_slice(int dv, int buffers) {
+    int cap = buffers == 4 ? 128 : 256;
+    return dv <= cap ? dv : cap;
 }
 
-static size_t mm_smem_bytes(int d, int dv, bool alias, int buffers) {
-    int bn = mm_key_tile(d, dv, alias);
-    size_t stage = (size_t)bn * (d + MM_PAD) + (alias ? 0 : (size_t)bn * (mm_slice(dv) + MM_PAD));
+static size_t mm_smem_for(int d, int slice, bool alias, int buffers, int bn) {
+    size_t stage = (size_t)bn * (d + MM_PAD) + (alias ? 0 : (size_t)bn * (slice + MM_PAD));
     size_t bytes = (size_t)buffers * stage * sizeof(__nv_bfloat16);
-    size_t merge = (size_t)(3 * 16 * mm_slice(dv) + 3 * 16 * 2) * sizeof(float);           // the partial rows of a shared walk
+    size_t merge = (size_t)(3 * 16 * slice + 3 * 16 * 2) * sizeof(float);           // the partial rows of a shared walk
     if (buffers == 4 && bytes < merge) bytes = merge;
     return (size_t)MM_BM * (d + MM_PAD) * sizeof(__nv_bfloat16) + bytes;
+}
+
+// Keys a tile.  Two buffers (prompts): 64, or 32 where tiles of 64 would leave room for fewer than the three blocks an SM that
+// the registers allow (the kernel hides its latencies by the number of blocks an SM holds; measured on 2,048 tokens with heads
+// of 128: 323 -> 272 us).  Four buffers (a step of single tokens, one block an SM): 64 wherever four of them fit, since fewer,
+// larger tiles are fewer rounds of the warps (62 against 72 us).
+static int mm_key_tile(int d, int slice, bool alias, int buffers) {
+    if (buffers == 4) return mm_smem_for(d, slice, alias, 4, 64) <= 200 * 1024 ? 64 : 32;
+    return mm_smem_for(d, slice, alias, 2, 64) > 72 * 1024 ? 32 : 64;
+}
+
+static size_t mm_smem_bytes(int d, int slice, bool alias, int buffers) {
+    return mm_smem_for(d, slice, alias, buffers, mm_key_tile(d, slice, alias, buffers));
 }
 
 // alias != 0: the value pool is the key pool (values = the key rows' leading dv elements)
 extern "C" int ce_masked_attention_mma_supported(int d, int dv, int q_stride, int q_head, int ldk, int ldv, int alias) {
     if (d < 16 || d % 16 || dv < 16 || dv % 16 || q_stride % 8 || q_head % 8 || ldk % 8 || ldv % 8) return 0;
     if (alias && dv > d) return 0;
-    return mm_smem_bytes(d, dv, alias != 0, 2) <= 200 * 1024;
+    return mm_smem_bytes(d, mm_slice(dv, 4), alias != 0, 2) <= 200 * 1024;
 }
 
 template <int DVT, bool ALIAS, int BN>
@@ -435,24 +447,29 @@ extern "C" int ce_masked_attention_mma(const void* q, const void* k_pool, const 
     int group = nh / nkv, pack = 1;
     if ((long long)n_tokens * 4 <= (long long)n_tiles * MM_BM)          // at most 16 tokens a tile on average
         while (pack < 16 && group % (pack * 2) == 0) pack *= 2;
-    int slice = mm_slice(dv);
-    MaskedMmaArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, (const __nv_bfloat16*)gate,
-                    (__nv_bfloat16*)out, positions, seq_slot, q_start, block_table, tiles, status, nh, nkv, d, dv, q_stride, q_head,
-                    ldk, ldv, gate_stride, page_size, max_pages, num_pages, window, keep_first, pack, slice, 0, scale, softcap};
-    dim3 grid(n_tiles * pack, nh / pack, (dv + slice - 1) / slice);
     // Few blocks (a step of single tokens): four buffers, so that the warps can take four tiles of keys side by side.  Blocks
     // of a packed tile that hold no token leave at once, so what counts is the tiles, not the grid.
-    int buffers = 2;
-    if ((long long)n_tiles * grid.y * grid.z <= (long long)ce_sm_count() && mm_smem_bytes(d, dv, alias, 4) <= 200 * 1024) buffers = 4;
-    a.share = buffers == 4;
-    size_t smem = mm_smem_bytes(d, dv, alias, buffers);
-    int bn = mm_key_tile(d, dv, alias);
+    int buffers = 2, slice = mm_slice(dv, 4);
+    if ((long long)n_tiles * (nh / pack) * ((dv + slice - 1) / slice) <= (long long)ce_sm_count() &&
+        mm_smem_bytes(d, slice, alias, 4) <= 200 * 1024) buffers = 4;
+    if (buffers == 2) {
+        slice = mm_slice(dv, 2);
+        if (mm_smem_bytes(d, slice, alias, 2) > 200 * 1024) slice = mm_slice(dv, 4);
+    }
+    MaskedMmaArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, (const __nv_bfloat16*)gate,
+                    (__nv_bfloat16*)out, positions, seq_slot, q_start, block_table, tiles, status, nh, nkv, d, dv, q_stride, q_head,
+                    ldk, ldv, gate_stride, page_size, max_pages, num_pages, window, keep_first, pack, slice, buffers == 4, scale, softcap};
+    dim3 grid(n_tiles * pack, nh / pack, (dv + slice - 1) / slice);
+    size_t smem = mm_smem_bytes(d, slice, alias, buffers);
+    int bn = mm_key_tile(d, slice, alias, buffers);
     if (alias) {
         if (slice <= 64) mm_launch_bn<8, true>(a, bn, grid, smem, stream);
-        else mm_launch_bn<16, true>(a, bn, grid, smem, stream);
+        else if (slice <= 128) mm_launch_bn<16, true>(a, bn, grid, smem, stream);
+        else mm_launch_bn<32, true>(a, bn, grid, smem, stream);
     } else {
         if (slice <= 64) mm_launch_bn<8, false>(a, bn, grid, smem, stream);
-        else mm_launch_bn<16, false>(a, bn, grid, smem, stream);
+        else if (slice <= 128) mm_launch_bn<16, false>(a, bn, grid, smem, stream);
+        else mm_launch_bn<32, false>(a, bn, grid, smem, stream);
     }
     return ce_check_launch("ce_masked_attention_mma");
 }

@@ -78,9 +78,9 @@ CASES["T"] = config([attention(heads=4, kv_heads=2, dim=32, vdim=64, window=37, 
                      delta(heads=2, kv_heads=2, dim=32, vdim=48, conv=3, a_rank=8, g_rank=8),
                      attention(heads=2, kv_heads=2, dim=16, vdim=64, window=100, keep_first=0, v_mix=True, scale=0.25, softcap=0)],
                     width=64, vocab=151, side=8)
-# The head sizes of a mid-sized model: keys and values of 128, a latent of 256 + 32, state heads of 64 x 128
+# The head sizes of a mid-sized model: keys of 128, values wider than a slice of 128, a latent of 256 + 32, state heads of 64 x 128
 CASES["V"] = config([latent(heads=4, dim=64, rot_dim=32, rot_dims=32, vdim=64, q_rank=96, kv_rank=256, window=90, scale=0.1, ff=384),
-                     attention(heads=4, kv_heads=1, dim=128, vdim=128, window=50, keep_first=8, scale=0.09, softcap=12.0),
+                     attention(heads=4, kv_heads=1, dim=128, vdim=144, window=50, keep_first=8, scale=0.09, softcap=12.0),
                      delta(heads=2, kv_heads=1, dim=64, vdim=128, conv=4, a_rank=16, g_rank=16)],
                     width=256, vocab=300, side=16)
 #: one layer of one kind each, for looking at a mechanism alone
